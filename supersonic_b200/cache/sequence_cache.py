@@ -36,6 +36,9 @@ class KvNeed:
     window: Optional[int] = None       # None: every earlier key stays
     value_dim: Optional[int] = None    # width of a value row; None: head_dim; 0: no value store (a mixer
                                        # whose values are part of its key rows, such as a cached latent)
+    keep_first: int = 0                # tokens at a sequence's start whose pages a window never gives back
+    tokens_per_row: int = 1            # P > 1: a store with one row per finished run of P tokens (pooled keys and
+                                       # values): a sequence of n tokens holds n // P rows, row b in page b // 64
 
     @property
     def v_dim(self) -> int:
@@ -122,8 +125,17 @@ class KvGroup:
     """Storage of the cache entries that share one need.  Which pages a slot holds is kept by the
     cache's native book, which writes the page ids into ``table_host``; ``pool`` and ``held`` show it."""
 
+    @staticmethod
+    def pages_of_need(need: KvNeed, n_pages: int, max_slots: int) -> int:
+        """Pages of a group's pool: ``n_pages``, or for a store of one row per run of tokens its share of them plus
+        a partly filled page per slot."""
+        if need.tokens_per_row <= 1:
+            return n_pages
+        return min(n_pages, (n_pages + need.tokens_per_row - 1) // need.tokens_per_row + max_slots)
+
     def __init__(self, need: KvNeed, entries: List[int], n_pages: int, max_slots: int,
                  pages_per_seq: int, dtype: torch.dtype, device: torch.device):
+        n_pages = self.pages_of_need(need, n_pages, max_slots)
         self.need = need
         self.entries = list(entries)
         self.index_of = {e: i for i, e in enumerate(self.entries)}
@@ -195,8 +207,14 @@ class SequenceCache:
             KvGroup(need, entries, self.n_pages, self.max_slots, self.pages_per_seq, dtype, device)
             for need, entries in by_need.items()]
         # who holds which slot and page: the native book, which fills the groups' host page tables
+        for g in self.kv_groups:
+            if g.need.tokens_per_row < 1 or g.need.keep_first < 0:
+                raise CacheError(f"a store's tokens_per_row must be at least 1 and keep_first not negative: {g.need}")
         self._book = CacheBook([g.need.window for g in self.kv_groups], self.n_pages, self.pages_per_seq,
-                               self.max_slots, self.max_seq_tokens, [g.table_host.numpy() for g in self.kv_groups])
+                               self.max_slots, self.max_seq_tokens, [g.table_host.numpy() for g in self.kv_groups],
+                               keep_first=[g.need.keep_first for g in self.kv_groups],
+                               strides=[g.need.tokens_per_row for g in self.kv_groups],
+                               group_pages=[g.n_pages for g in self.kv_groups])
         for i, g in enumerate(self.kv_groups):
             g.bind(self._book, i)
         self.slots = _Slots(self._book, self.max_slots)
@@ -219,7 +237,8 @@ class SequenceCache:
         seen = set()
         for need in flatten_needs(needs).values():
             if isinstance(need, KvNeed):
-                total += n_pages * need.n_kv_heads * PAGE_TOKENS * (need.head_dim + need.v_dim) * item
+                total += KvGroup.pages_of_need(need, n_pages, slots) * need.n_kv_heads * PAGE_TOKENS \
+                    * (need.head_dim + need.v_dim) * item
                 if need not in seen:                                       # one page table a group
                     seen.add(need)
                     total += slots * pages_per_seq * 4
@@ -307,7 +326,7 @@ class SequenceCache:
         return self._state[cache_id]
 
     def free_tokens(self) -> int:
-        return min((g.pool.n_free for g in self.kv_groups), default=self.n_pages) * PAGE_TOKENS
+        return min((g.pool.n_free * g.need.tokens_per_row for g in self.kv_groups), default=self.n_pages) * PAGE_TOKENS
 
     def bytes_read_for(self, slot: int) -> int:
         """Bytes of keys and values an attention over ``slot`` reads now: every cache entry, the
@@ -315,7 +334,9 @@ class SequenceCache:
         n = self.length(slot)
         total = 0
         for g in self.kv_groups:
-            tokens = n if g.need.window is None else min(n, g.need.window)
+            tokens = n // g.need.tokens_per_row
+            if g.need.window is not None:
+                tokens = min(tokens, g.need.window + min(g.need.keep_first, max(tokens - g.need.window, 0)))
             total += len(g.entries) * tokens * g.need.n_kv_heads * (g.need.head_dim + g.need.v_dim) * g.k.element_size()
         return total + sum(t.shape[1] * 4 for t in self._state.values())
 

@@ -16,6 +16,7 @@ from typing import Any, Dict, Type
 from .base import ConfigError, ModelSpec
 from .llama import ARCHITECTURE as _LLAMA, LlamaConfig
 from .sotavik import ARCHITECTURE as _SOTAVIK, SotavikConfig
+from .ronelorn import ARCHITECTURE as _RONELORN, RonelornConfig
 from .vufadra import ARCHITECTURE as _VUFADRA, VufadraConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
@@ -68,6 +69,7 @@ def spec_from_config(config) -> ModelSpec:
 register_architecture(_LLAMA, LlamaConfig)
 register_architecture(_SOTAVIK, SotavikConfig)
 register_architecture(_VUFADRA, VufadraConfig)
+register_architecture(_RONELORN, RonelornConfig)
 
 
 _PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets")

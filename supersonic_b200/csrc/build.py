@@ -49,6 +49,8 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "expert_ops": {"sources": ["expert_ops.cu"], "flags": [], "link": []},
     "sequence_ops": {"sources": ["sequence_ops.cu"], "flags": [], "link": []},
     "gated_attention": {"sources": ["gated_attention.cu"], "flags": [], "link": []},
+    "window_attention": {"sources": ["window_attention.cu"], "flags": [], "link": []},
+    "mingru_ops": {"sources": ["mingru_ops.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
     # the host side's native core: no CUDA in it, so it is compiled by the C++ compiler alone
     "host_runtime": {"sources": ["runtime.cpp"], "flags": [], "link": [], "dir": os.path.join(os.path.dirname(_HERE), "host"),

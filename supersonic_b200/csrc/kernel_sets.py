@@ -222,6 +222,62 @@ class PlainKernels:
         ops.sigmoid_attention_plain(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, bias, out, n_q,
                                     n_kv, dim, vdim, page_shift, chunk, window, scale, pdl=self._chain(batch.n_tokens))
 
+    # ---- softmax attention over a window, kept first tokens and pooled runs ---------------------
+    def activation(self, u, out, kind, scale=1.0):
+        """out = act(u) * scale (``relu_squared``, ``gelu_tanh``, ``silu``)."""
+        ops.activation(u, out, kind, scale, pdl=self._chain(u.shape[0]))
+
+    def linear_activation(self, x, weight, out, kind, scale=1.0):
+        """out = act(x @ weight^T) * scale."""
+        x = as_tensor(x)
+        u = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        self.linear(x, weight, u)
+        self.activation(u, out, kind, scale)
+
+    def qkv_prepare(self, qkv, q_weight, k_weight, norm, eps, position, value_position, kv, batch, n_q, n_kv, dim, vdim,
+                    page_shift, write_cache=True):
+        """Norm of q and k (``norm`` ``"head"``, ``"row"`` or None), rotation of their first coordinates by
+        ``position``, of the values over their whole width by ``value_position`` (either may be None), k and v into
+        the cache."""
+        cos = sin = vcos = vsin = None
+        rot_dims, inter, v_inter = 0, False, False
+        if position is not None:
+            position.check_range(batch)
+            cos, sin, rot_dims = position.rotary_tables()
+            inter = bool(getattr(position, "interleaved", False))
+        if value_position is not None:
+            value_position.check_range(batch)
+            vcos, vsin, _ = value_position.rotary_tables()
+            v_inter = bool(getattr(value_position, "interleaved", False))
+        k_cache, v_cache, table, _ = kv
+        ops.qkv_prepare(qkv, q_weight, k_weight, norm, eps, cos, sin, rot_dims, inter, vcos, vsin, v_inter, batch.pos,
+                        batch.slot_of_token, table, k_cache, v_cache, n_q, n_kv, dim, vdim, page_shift, write_cache,
+                        pdl=self._chain(batch.n_tokens))
+
+    def pool_rows(self, kv, pooled_kv, batch, n_kv, dim, vdim, page_shift, pool):
+        """The mean key and value row of every run of ``pool`` tokens that the step's tokens finish."""
+        k_cache, v_cache, table, _ = kv
+        pk, pv, ptable, _ = pooled_kv
+        ops.pool_rows(k_cache, v_cache, table, pk, pv, ptable, batch.cu_new, batch.seq_start, batch.seq_slot,
+                      batch.max_new, n_kv, dim, vdim, page_shift, pool, pdl=self._chain(batch.n_tokens))
+
+    def window_attention(self, q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool,
+                         scale, softcap, sinks, value_position, out_scale=1.0):
+        vcos = vsin = None
+        v_inter = False
+        if value_position is not None:
+            vcos, vsin, _ = value_position.rotary_tables()
+            v_inter = bool(getattr(value_position, "interleaved", False))
+        k_cache, v_cache, table, _ = kv
+        pooled = None if pooled_kv is None else pooled_kv[:3]
+        ops.window_attention_plain(q, k_cache, v_cache, table, pooled, batch.pos, batch.slot_of_token, out, n_q, n_kv,
+                                   dim, vdim, page_shift, window, keep_first, pool, scale, softcap, sinks, vcos, vsin,
+                                   v_inter, out_scale, pdl=self._chain(batch.n_tokens))
+
+    def mingru_scan(self, proj, z_bias, x_bias, state, batch, out, width, out_scale=1.0):
+        ops.mingru_scan(proj, z_bias, x_bias, state, batch.cu_new, batch.seq_slot, out, width, out_scale,
+                        tiled=batch.max_new >= ops.MINGRU_TILED_MIN_NEW, pdl=self._chain(batch.n_tokens))
+
     # ---- experts ---------------------------------------------------------------------
     expert_tile_rows = 64
 

@@ -873,6 +873,185 @@ def sigmoid_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         c_int(int(window) if window else 0), c_float(scale), c_int(1 if pdl else 0), _stream()), "sigmoid_attention_plain")
 
 
+# ---- softmax attention over a window, kept first tokens and pooled runs ---------------------------
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(u: torch.Tensor, out: torch.Tensor, kind: str, scale: float = 1.0, pdl: bool = False) -> None:
+    """out[t, c] = act(u[t, c]) * scale in float32 arithmetic; ``kind``: ``relu_squared`` (relu(u)^2),
+    ``gelu_tanh`` (0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)))) or ``silu``."""
+    _need(u, "u", None, 2); _need(out, "out", u.dtype, 2)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not known (known: {sorted(ACTIVATIONS)})")
+    if tuple(out.shape) != tuple(u.shape):
+        raise KernelError("activation: out must have u's shape")
+    _check(_fn("plain_ops", "ssb_activation")(
+        _ptr(u), c_int(u.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(u.dtype)), c_int(u.shape[0]),
+        c_int(u.shape[1]), c_int(ACTIVATIONS[kind]), c_float(scale), c_int(1 if pdl else 0), _stream()), "activation")
+
+
+QK_NORM_MODES = {None: 0, "none": 0, "head": 1, "row": 2}
+
+
+def _rotation_tables(cos, sin, dims: int, what: str) -> int:
+    _need(cos, what + " cos", torch.float32, 2); _need(sin, what + " sin", torch.float32, 2)
+    if cos.shape != sin.shape or cos.shape[1] * 2 != dims or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise KernelError(f"{what}: cos/sin must be [positions, {dims}/2], contiguous")
+    return cos.shape[0]
+
+
+def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], norm: Optional[str],
+                eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dims: int, interleaved: bool,
+                v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_interleaved: bool, pos: torch.Tensor,
+                slot: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int,
+                n_kv: int, dim: int, vdim: int, page_shift: int, write_cache: bool = True, pdl: bool = False) -> None:
+    """Rows [q (n_q x dim) | k (n_kv x dim) | v (n_kv x vdim)].  ``norm`` ``"head"``: every q and k head is divided
+    by its root mean square (eps inside the root) and multiplied by a weight vector [dim] shared by the heads;
+    ``"row"``: all heads of q (of k) together are divided by one root mean square, weights [heads x dim]; None:
+    no norm.  Then the first ``rot_dims`` coordinates of every q and k head are turned by the token's position, and
+    with ``v_cos``/``v_sin`` [positions, vdim / 2] every value head over its whole width.  q is written back in
+    place; k and v go to the token's place in the paged cache."""
+    _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    if norm not in QK_NORM_MODES:
+        raise KernelError(f"qkv_prepare: norm {norm!r} is not known ('head', 'row' or None)")
+    mode = QK_NORM_MODES[norm]
+    T = qkv.shape[0]
+    if qkv.shape[1] < n_q * dim + (n_kv * (dim + vdim) if write_cache else 0) or pos.shape[0] != T or slot.shape[0] != T:
+        raise KernelError("qkv_prepare: rows are too narrow, or not one position and slot per token")
+    if mode:
+        for w, heads in ((q_weight, n_q), (k_weight, n_kv)):
+            _need(w, "norm weight", torch.float32, 1)
+            if w.shape[0] != (dim if mode == 1 else heads * dim):
+                raise KernelError("qkv_prepare: a norm weight per coordinate of a head ('head') or of the row ('row')")
+    else:
+        q_weight = k_weight = None
+    positions = 0
+    if cos is not None and rot_dims:
+        positions = _rotation_tables(cos, sin, rot_dims, "qkv_prepare")
+    else:
+        cos = sin = None
+        rot_dims = 0
+    if v_cos is not None:
+        v_positions = _rotation_tables(v_cos, v_sin, vdim, "qkv_prepare values")
+        positions = v_positions if cos is None else min(positions, v_positions)
+    if write_cache:
+        _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype)
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()) or k_cache.shape[-1] != dim or v_cache.shape[-1] != vdim:
+            raise KernelError("qkv_prepare: cache rows of dim and vdim, contiguous")
+    _check(_fn("window_attention", "ssb_qkv_prepare")(
+        _ptr(qkv), c_int(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), _ptr(q_weight), _ptr(k_weight), c_int(mode),
+        c_float(eps), _ptr(cos), _ptr(sin), c_int(rot_dims), c_int(1 if interleaved else 0), _ptr(v_cos), _ptr(v_sin),
+        c_int(1 if v_interleaved else 0), c_int(positions), _ptr(pos), _ptr(slot), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim),
+        c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if pdl else 0), _stream()), "qkv_prepare")
+
+
+def pool_rows(k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, pk_cache: torch.Tensor,
+              pv_cache: torch.Tensor, pool_table: torch.Tensor, cu_new: torch.Tensor, seq_start: torch.Tensor,
+              seq_slot: torch.Tensor, max_new: int, n_kv: int, dim: int, vdim: int, page_shift: int, pool: int,
+              pdl: bool = False) -> None:
+    """For every run of ``pool`` tokens that a sequence's new tokens finish: the mean of the run's cached key rows
+    (and value rows), summed in rising order in float32, into row ``run`` of the pooled store."""
+    for t, n in ((k_cache, "k_cache"), (v_cache, "v_cache"), (pk_cache, "pk_cache"), (pv_cache, "pv_cache")):
+        _need(t, n, k_cache.dtype)
+        if not t.is_contiguous():
+            raise KernelError(f"pool_rows: {n} must be contiguous")
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2); _need(pool_table, "pool_table", torch.int32, 2)
+    B = seq_slot.shape[0]
+    if cu_new.shape[0] != B + 1 or seq_start.shape[0] != B or k_cache.shape[-1] != dim or pk_cache.shape[-1] != dim \
+            or v_cache.shape[-1] != vdim or pv_cache.shape[-1] != vdim or pool < 1:
+        raise KernelError("pool_rows: shapes")
+    _check(_fn("window_attention", "ssb_pool_rows")(
+        _ptr(k_cache), _ptr(v_cache), _ptr(page_table), c_int(page_table.shape[1]), _ptr(pk_cache), _ptr(pv_cache),
+        _ptr(pool_table), c_int(pool_table.shape[1]), c_int(dtype_code(k_cache.dtype)), _ptr(cu_new), _ptr(seq_start),
+        _ptr(seq_slot), c_int(B), c_int(max_new), c_int(n_kv), c_int(dim), c_int(vdim), c_int(page_shift), c_int(pool),
+        c_int(1 if pdl else 0), _stream()), "pool_rows")
+
+
+def _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim, window, keep_first, pool,
+                           sinks, v_cos, v_sin, what):
+    _need(q, "q", None, 2); _need(out, "out", q.dtype, 2); _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
+    _need(page_table, "page_table", torch.int32, 2)
+    T = q.shape[0]
+    if out.shape[0] != T or out.shape[1] < n_q * vdim or q.shape[1] < n_q * dim or n_q % n_kv \
+            or k_cache.shape[-1] != dim or v_cache.shape[-1] != vdim:
+        raise KernelError(f"{what}: q/out/cache shapes")
+    pk = pv = ptable = None
+    if pool:
+        if not window:
+            raise KernelError(f"{what}: pooled runs stand for what has left a window: a window is needed")
+        pk, pv, ptable = pooled
+        _need(pk, "pooled keys", q.dtype); _need(pv, "pooled values", q.dtype); _need(ptable, "pooled page table", torch.int32, 2)
+        if pk.shape[-1] != dim or pv.shape[-1] != vdim:
+            raise KernelError(f"{what}: pooled rows of dim and vdim")
+    if sinks is not None and not isinstance(sinks, bool):
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != n_q:
+            raise KernelError(f"{what}: one sink per query head")
+    positions = 0
+    if v_cos is not None:
+        positions = _rotation_tables(v_cos, v_sin, vdim, what + " values")
+    return pk, pv, ptable, positions
+
+
+def window_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                           pooled, pos: torch.Tensor, slot: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, dim: int,
+                           vdim: int, page_shift: int, window: Optional[int], keep_first: int, pool: int, scale: float,
+                           softcap: Optional[float], sinks, v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor],
+                           v_interleaved: bool, out_scale: float = 1.0, pdl: bool = False) -> None:
+    """Softmax attention of every token over its slot's cache: the keys j with pos - window < j <= pos, the first
+    ``keep_first`` tokens, and (``pool`` > 0, ``pooled`` = (keys, values, page table) of the pooled store) the
+    pooled row of every run of ``pool`` tokens that ends at or before pos - window.  Scores times ``scale``, then
+    ``softcap * tanh(s / softcap)`` if a cap is given.  ``sinks``: None, True (a sink of score 0 in the
+    denominator) or one float per query head.  With ``v_cos``/``v_sin`` the head's sum is turned back by the
+    token's position.  ``out`` is multiplied by ``out_scale``."""
+    pk, pv, ptable, positions = _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim,
+                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention")
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    zero_sink = sinks is True
+    _check(_fn("window_attention", "ssb_window_attention_plain")(
+        _ptr(q), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(pk), _ptr(pv), _ptr(ptable), c_int(ptable.shape[1] if ptable is not None else 0),
+        _ptr(pos), _ptr(slot), _ptr(out), c_int(out.stride(0)), c_int(q.shape[0]), c_int(n_q), c_int(n_kv), c_int(dim),
+        c_int(vdim), c_int(page_shift), c_int(int(window) if window else 0), c_int(int(keep_first or 0)),
+        c_int(int(pool or 0)), c_float(scale), c_float(float(softcap) if softcap else 0.0),
+        _ptr(None if (sinks is None or isinstance(sinks, bool)) else sinks), c_int(1 if zero_sink else 0), _ptr(v_cos),
+        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(1 if pdl else 0),
+        _stream()), "window_attention_plain")
+
+
+# ---- minGRU --------------------------------------------------------------------------------
+MINGRU_TILED_MIN_NEW = 64
+
+
+def mingru_scan(proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
+                cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, width: int, out_scale: float = 1.0,
+                tiled: bool = False, pdl: bool = False) -> None:
+    """Rows of ``proj`` are [zp | up | gp], ``width`` columns each.  Per channel, over every sequence's new tokens
+    from and into its row of ``state`` [slots, width] (float32): z = sigmoid(zp + bz), cand = up + bu + 1/2 where
+    up + bu >= 0 and sigmoid(up + bu) below, S <- (1 - z) S + z cand, out = out_scale * S * silu(gp).  ``tiled``:
+    the form that spreads a run of tokens over the warps of a block (even width and strides)."""
+    _need(proj, "proj", None, 2); _need(out, "out", None, 2); _need(state, "state", torch.float32, 2)
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    B = seq_slot.shape[0]
+    if proj.shape[1] < 3 * width or out.shape[1] < width or out.shape[0] != proj.shape[0] or state.shape[1] != width \
+            or cu_new.shape[0] != B + 1 or not state.is_contiguous():
+        raise KernelError("mingru_scan: shapes")
+    for b in (z_bias, x_bias):
+        if b is not None:
+            _need(b, "bias", torch.float32, 1)
+            if b.shape[0] != width:
+                raise KernelError("mingru_scan: a bias per channel")
+    if tiled and (width % 2 or proj.stride(0) % 2 or out.stride(0) % 2 or proj.data_ptr() % 8 or out.data_ptr() % 8):
+        tiled = False
+    _check(_fn("mingru_ops", "ssb_mingru_scan")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), _ptr(z_bias), _ptr(x_bias), _ptr(state),
+        _ptr(cu_new), _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B), c_int(width),
+        c_float(out_scale), c_int(1 if tiled else 0), c_int(1 if pdl else 0), _stream()), "mingru_scan")
+
+
 # ---- experts -----------------------------------------------------------------------------
 def route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, expert_of: torch.Tensor,
                 pair_weight: torch.Tensor, pdl: bool = False) -> None:

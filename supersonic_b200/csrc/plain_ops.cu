@@ -443,6 +443,46 @@ SSB_API int ssb_swiglu(const void* gate_up, int ld, void* z, int ldz, int dtype,
 }
 
 // ---------------------------------------------------------------------------------------
+// An activation between two dense products: z[t, c] = act(u[t, c]) * scale, in float32.
+//   kind 0: relu(u)^2;  1: gelu with tanh, 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)));  2: silu
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float ssb_activate(float u, int kind) {
+    if (kind == 0) { const float r = fmaxf(u, 0.f); return r * r; }
+    if (kind == 1) return 0.5f * u * (1.0f + tanhf(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+    return u / (1.0f + expf(-u));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ u, int ld, T* __restrict__ z, int ldz, int width, size_t total,
+                                  int kind, float scale) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / width;
+    const int c = (int)(idx % width);
+    z[t * ldz + c] = ssb_from_float<T>(ssb_activate(ssb_to_float(u[t * ld + c]), kind) * scale);
+}
+
+SSB_API int ssb_activation(const void* u, int ld, void* z, int ldz, int dtype, int n_tokens, int width, int kind,
+                           float scale, int pdl, cudaStream_t stream) {
+    if (kind < 0 || kind > 2) return SSB_ERR_BAD_SIZE;
+    const size_t total = (size_t)n_tokens * width;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, pdl != 0, (const float*)u, ld, (float*)z,
+                        ldz, width, total, kind, scale);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, pdl != 0, (const bf16*)u, ld, (bf16*)z,
+                        ldz, width, total, kind, scale);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
 // out (float32) += x
 // ---------------------------------------------------------------------------------------
 template <typename T>

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import POINTER, c_char_p, c_int, c_int32, c_longlong, c_void_p
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -46,6 +46,7 @@ def lib() -> ctypes.CDLL:
             "ssb_free_list_is_held": (c_int, [c_void_p, c_int]),
             "ssb_free_list_check": (c_int, [c_void_p]),
             "ssb_cache_book_new": (c_void_p, [c_int, int_p, c_int, c_int, c_int, c_longlong]),
+            "ssb_cache_book_new_groups": (c_void_p, [c_int, int_p, int_p, int_p, int_p, c_int, c_int, c_int, c_longlong]),
             "ssb_cache_book_delete": (None, [c_void_p]),
             "ssb_cache_book_error": (c_char_p, [c_void_p]),
             "ssb_cache_book_bind_table": (c_int, [c_void_p, c_int, c_void_p]),
@@ -151,12 +152,22 @@ class CacheBook:
     """Who holds which slot and which pages, for every group of cache entries: see ``runtime.cpp``.
     ``windows[g]`` is group g's window in tokens or None; ``tables[g]`` its page table on the host, an
     int32 array ``[max_slots, pages_per_seq]`` (for instance the numpy view of a pinned tensor) that the
-    book writes the ids of reserved pages into."""
+    book writes the ids of reserved pages into.  Per group, optionally: ``keep_first[g]`` rows at a sequence's
+    start that its window never gives back; ``strides[g]`` tokens that one row stands for (a store with a row per
+    finished run of that many tokens: n tokens make n // stride rows); ``group_pages[g]`` pages of its own pool
+    (default ``n_pages``)."""
 
     def __init__(self, windows: Sequence, n_pages: int, pages_per_seq: int, max_slots: int, max_seq_tokens: int,
-                 tables: Sequence[np.ndarray]):
+                 tables: Sequence[np.ndarray], keep_first: Optional[Sequence] = None, strides: Optional[Sequence] = None,
+                 group_pages: Optional[Sequence] = None):
         w = _ints([int(x) if x else 0 for x in windows])
-        h = lib().ssb_cache_book_new(len(windows), w, n_pages, pages_per_seq, max_slots, max_seq_tokens)
+        n = len(windows)
+        keep = _ints([int(x) if x else 0 for x in (keep_first if keep_first is not None else [0] * n)])
+        stride = _ints([int(x) if x else 1 for x in (strides if strides is not None else [1] * n)])
+        pages = _ints([int(x) if x else 0 for x in (group_pages if group_pages is not None else [0] * n)])
+        if len(keep) != n or len(stride) != n or len(pages) != n:
+            raise CacheError("one kept-rows figure, stride and page count per group")
+        h = lib().ssb_cache_book_new_groups(n, w, keep, stride, pages, n_pages, pages_per_seq, max_slots, max_seq_tokens)
         if not h:
             raise CacheError("the cache needs at least one page, one slot and room for one token")
         self._h = c_void_p(h)

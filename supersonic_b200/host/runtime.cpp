@@ -93,15 +93,22 @@ private:
 // ids, and per slot which page of its sequence lives in which of them.  The page table rows are
 // written into memory the caller owns (pinned host memory that is copied to the device).
 struct Group {
-    int window;                                   // 0: every earlier key stays
+    int window;                                   // 0: every earlier key stays (counted in rows)
+    int keep_first;                               // rows at a sequence's start that a window never gives back
+    int stride;                                   // tokens a row stands for: 1, or P for a store that holds one row per
+                                                  // finished run of P tokens (a sequence of n tokens has n / P rows)
     FreeList pool;
     std::vector<std::map<int, int>> held;         // per slot: page index within the sequence -> page id
     int32_t* table = nullptr;                     // [max_slots, pages_per_seq]
     int dirty_lo, dirty_hi;
-    Group(int window_, int n_pages, int max_slots)
-        : window(window_), pool(n_pages, "page"), held(max_slots), dirty_lo(max_slots), dirty_hi(-1) {}
+    Group(int window_, int n_pages, int max_slots, int keep_first_ = 0, int stride_ = 1)
+        : window(window_), keep_first(keep_first_ > 0 ? keep_first_ : 0), stride(stride_ > 1 ? stride_ : 1),
+          pool(n_pages, "page"), held(max_slots), dirty_lo(max_slots), dirty_hi(-1) {}
 
-    // First page a query at a position >= length can still read.
+    long long rows_of(long long tokens) const { return tokens / stride; }
+    // Pages at a sequence's start that stay whatever the window says.
+    int kept_pages() const { return pages_for(keep_first); }
+    // First page a query at a position >= length can still read (the kept first pages aside).
     int first_needed_page(long long length) const {
         if (window <= 0) return 0;
         const long long lo = length - window + 1;
@@ -112,6 +119,8 @@ struct Group {
     // only the last held page and those after it need a look.
     void missing_pages(int slot, long long length, long long new_length, std::vector<int>& out) const {
         out.clear();
+        length = rows_of(length);
+        new_length = rows_of(new_length);
         int first = first_needed_page(length);
         if (length > 0) first = std::max(first, pages_for(length) - 1);
         const auto& h = held[slot];
@@ -129,11 +138,15 @@ struct CacheBook {
     std::string error;
     std::vector<int> scratch;
 
-    CacheBook(int n_groups, const int* windows, int n_pages_, int pages_per_seq_, int max_slots_, long long max_seq)
+    // keep_first, strides, group_pages: per group, or null for none / 1 / n_pages
+    CacheBook(int n_groups, const int* windows, int n_pages_, int pages_per_seq_, int max_slots_, long long max_seq,
+              const int* keep_first = nullptr, const int* strides = nullptr, const int* group_pages = nullptr)
         : n_pages(n_pages_), pages_per_seq(pages_per_seq_), max_slots(max_slots_), max_seq_tokens(max_seq),
           slots(max_slots_, "slot"), length(max_slots_, 0) {
         groups.reserve(n_groups);
-        for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], n_pages_, max_slots_);
+        for (int g = 0; g < n_groups; ++g)
+            groups.emplace_back(windows[g], group_pages && group_pages[g] > 0 ? group_pages[g] : n_pages_, max_slots_,
+                                keep_first ? keep_first[g] : 0, strides ? strides[g] : 1);
     }
 
     int need_held(int slot) {
@@ -157,7 +170,7 @@ struct CacheBook {
                                PAGE_TOKENS, g.pool.n_free(), g.pool.capacity());
                 return SSB_HOST_FULL;
             }
-            if (!scratch.empty() && pages_for(new_len) > pages_per_seq) {
+            if (!scratch.empty() && pages_for(g.rows_of(new_len)) > pages_per_seq) {
                 error = format("%lld tokens exceed the %d a sequence may hold", new_len, pages_per_seq * PAGE_TOKENS);
                 return SSB_HOST_FULL;
             }
@@ -184,11 +197,12 @@ struct CacheBook {
         length[slot] += n_new;
         for (auto& g : groups) {
             if (g.window <= 0) continue;
-            const int first = g.first_needed_page(length[slot]);
+            const int first = g.first_needed_page(g.rows_of(length[slot]));
             auto& h = g.held[slot];
-            while (!h.empty() && h.begin()->first < first) {
-                if (int rc = g.pool.give_back(h.begin()->second, error)) return rc;
-                h.erase(h.begin());
+            auto it = h.lower_bound(g.kept_pages());
+            while (it != h.end() && it->first < first) {
+                if (int rc = g.pool.give_back(it->second, error)) return rc;
+                it = h.erase(it);
             }
         }
         return SSB_HOST_OK;
@@ -210,6 +224,7 @@ struct CacheBook {
         if (int rc = slots.check(error)) return rc;
         for (auto& g : groups) {
             if (int rc = g.pool.check(error)) return rc;
+            const int n_pages = g.pool.capacity();
             std::vector<char> seen(n_pages, 0);
             int n_seen = 0;
             for (int s = 0; s < max_slots; ++s) {
@@ -256,6 +271,17 @@ SSB_HOST_API void* ssb_cache_book_new(int n_groups, const int* windows, int n_pa
                                       long long max_seq_tokens) {
     if (n_groups < 0 || n_pages <= 0 || pages_per_seq <= 0 || max_slots <= 0 || max_seq_tokens <= 0) return nullptr;
     return new CacheBook(n_groups, windows, n_pages, pages_per_seq, max_slots, max_seq_tokens);
+}
+// The same with, per group (each array may be null): rows at a sequence's start that a window never gives back,
+// the tokens a row stands for (a store with one row per finished run of that many tokens), and the group's own
+// number of pages.
+SSB_HOST_API void* ssb_cache_book_new_groups(int n_groups, const int* windows, const int* keep_first, const int* strides,
+                                             const int* group_pages, int n_pages, int pages_per_seq, int max_slots,
+                                             long long max_seq_tokens) {
+    if (n_groups < 0 || n_pages <= 0 || pages_per_seq <= 0 || max_slots <= 0 || max_seq_tokens <= 0) return nullptr;
+    for (int g = 0; g < n_groups; ++g)
+        if ((strides && strides[g] < 1) || (keep_first && keep_first[g] < 0) || (group_pages && group_pages[g] < 0)) return nullptr;
+    return new CacheBook(n_groups, windows, n_pages, pages_per_seq, max_slots, max_seq_tokens, keep_first, strides, group_pages);
 }
 SSB_HOST_API void ssb_cache_book_delete(void* b) { delete (CacheBook*)b; }
 SSB_HOST_API const char* ssb_cache_book_error(void* b) { return ((CacheBook*)b)->error.c_str(); }

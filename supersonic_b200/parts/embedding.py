@@ -11,10 +11,12 @@ from .registry import BuildContext, register_embedding
 
 @register_embedding("embedding")
 class Embedding:
-    """params: ``vocab_size``, ``hidden_size``; weights: ``weight`` [vocab, hidden]."""
+    """params: ``vocab_size``, ``hidden_size``, ``scale`` (optional: the rows are multiplied by it in float32);
+    weights: ``weight`` [vocab, hidden]."""
 
     def __init__(self, params, weights, build: BuildContext):
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
         self.table = build.weights.as_dtype(weights["weight"], build.dtype, share=True)
         if tuple(self.table.shape) != (self.vocab, self.hidden):
             raise ValueError(f"{weights['weight']} has shape {tuple(self.table.shape)}, "
@@ -23,6 +25,8 @@ class Embedding:
     def __call__(self, ctx, token_ids):
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
         ctx.kernels.embed(token_ids, self.table, out)
+        if self.scale != 1.0:
+            ctx.kernels.scale_(out, self.scale)
         return out
 
 

@@ -1,7 +1,7 @@
 """Feed-forwards.  ``swiglu``: down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g)),
 added to the residual (crates/runner/src/prefill_engine.rs:3226-3366;
 kernels/full_attention_cuda.cuh:1995-2010).  Gate and up run as one matrix product
-over row-concatenated weights."""
+over row-concatenated weights.  ``dense``: out_scale * down( act(up(x)) ) with a named activation."""
 from __future__ import annotations
 
 import torch
@@ -40,4 +40,38 @@ class SwiGLU:
     def forward(self, ctx, x, residual):
         z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
         ctx.kernels.gate_up_swiglu(x, self.w_gate_up, self.layout, z)
+        ctx.kernels.linear(z, self.w_down, residual, accumulate=True)
+
+
+@register_feed_forward("dense")
+class DenseFeedForward:
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` (``relu_squared``: relu(u)^2; ``gelu_tanh``;
+    ``silu``), ``out_scale`` (1.0: what the sublayer's output is multiplied by before it joins the stream; applied
+    to the activation's float32 result, before its one rounding); weights: ``up``, ``down``."""
+
+    takes_lazy_input = True
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "relu_squared"))
+        from ..csrc.ops import ACTIVATIONS
+        if self.activation not in ACTIVATIONS:
+            raise ValueError(f"dense feed-forward: activation {self.activation!r} is not known (known: {sorted(ACTIVATIONS)})")
+        self.out_scale = float(params.get("out_scale", 1.0))
+        w = build.weights
+        self.w_up = w.as_dtype(weights["up"], build.dtype)
+        self.w_down = w.as_dtype(weights["down"], build.dtype)
+        for name, t, want in ((weights["up"], self.w_up, (self.inter, self.hidden)),
+                              (weights["down"], self.w_down, (self.hidden, self.inter))):
+            if tuple(t.shape) != want:
+                raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {want}")
+        self.dtype = build.dtype
+
+    @staticmethod
+    def activation_elements(params) -> int:
+        return 2 * int(params["intermediate_size"])
+
+    def forward(self, ctx, x, residual):
+        z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
+        ctx.kernels.linear_activation(x, self.w_up, z, self.activation, self.out_scale)
         ctx.kernels.linear(z, self.w_down, residual, accumulate=True)

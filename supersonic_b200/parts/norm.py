@@ -11,7 +11,8 @@ from .registry import BuildContext, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm:
-    """params: ``size``, ``eps``; weights: ``weight`` [size].
+    """params: ``size``, ``eps``, ``unit_offset`` (False; True: the weight is stored around zero and the norm
+    multiplies by 1 + w, the sum taken in float32 and kept so); weights: ``weight`` [size].
 
     Interface of a norm: ``__call__(ctx, x, rows=None) -> tensor`` where ``x`` is the
     float32 residual stream ``[T, size]`` and the result has the activation dtype;
@@ -25,6 +26,8 @@ class RMSNorm:
         w = build.weights.stored(weights["weight"])
         # 32-bit weights stay 32-bit; in the float32 path everything is 32-bit
         self.weight = w.float() if build.dtype == torch.float32 else w
+        if params.get("unit_offset"):
+            self.weight = (w.float() + 1.0).contiguous()
         if tuple(self.weight.shape) != (self.size,):
             raise ValueError(f"rmsnorm weight has shape {tuple(self.weight.shape)}, expected ({self.size},)")
         self.dtype = build.dtype

@@ -24,6 +24,12 @@ previous token's input, m_s = h_t + (h_(t-1) - h_t) * mu_s:
     o = (S_(t-1) + diag(bonus) k v^T)^T r,      S_t = diag(w) S_(t-1) + k v^T
     result = Wo [rms(o_head) * norm * gate]
 
+``min_gru`` (a vector state per channel whose gates read the current token alone):
+
+    z = sigmoid(Wz h + bz),    u = Wx h + bx,    cand = u + 1/2 where u >= 0, sigmoid(u) where u < 0
+    S_t = (1 - z) S_(t-1) + z cand                                   S_(-1) = 0
+    result = out_scale * Wo (S_t * silu(Wg h))
+
 Decays, gates of the recurrences, unit keys, the states and o are float32 whatever the activation type; the
 matrix products and the convolution run in the activation type.
 """
@@ -234,4 +240,45 @@ class TimeMixing:
         k.matrix_state_scan(proj, self.r_off, self.k_off, self.v_off, z, "bonus", ctx.cache.state((cache_id, "state")),
                             ctx.batch, o, H, d, d, bonus=self.bonus)
         k.head_norm_gate(o, self.norm_w, self.eps, proj[:, self.g_off:], y, H, d, gate_kind="silu")
+        k.linear(y, self.w_o, residual, accumulate=True)
+
+
+@register_mixer("min_gru")
+class MinGRU:
+    """params: ``hidden_size``, ``width`` (channels), ``out_scale`` (1.0); weights: ``z``, ``z_bias``, ``x``, ``x_bias``,
+    ``g``, ``o``.  The three input products run as one over [z | x | g]."""
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.hidden, self.C = int(params["hidden_size"]), int(params["width"])
+        self.out_scale = float(params.get("out_scale", 1.0))
+        w, dt = build.weights, build.dtype
+        got = {r: w.as_dtype(weights[r], dt) for r in ("z", "x", "g", "o")}
+        got.update({r: w.stored(weights[r]).float().contiguous() for r in ("z_bias", "x_bias")})
+        C = self.C
+        _shapes(got, {"z": (C, self.hidden), "x": (C, self.hidden), "g": (C, self.hidden), "o": (self.hidden, C),
+                      "z_bias": (C,), "x_bias": (C,)}, weights)
+        self.w_in = torch.cat([got["z"], got["x"], got["g"]], dim=0).contiguous()
+        self.w_o = got["o"]
+        self.z_bias, self.x_bias = got["z_bias"], got["x_bias"]
+        self.dtype = dt
+
+    def cache_need(self):
+        return StateNeed(self.C)
+
+    @staticmethod
+    def cache_need_from(params):
+        return StateNeed(int(params["width"]))
+
+    @staticmethod
+    def activation_elements(params) -> int:
+        return 4 * int(params["width"])
+
+    def forward(self, ctx, x, residual, cache_id, writes_cache, position):
+        if not writes_cache:
+            raise ValueError("min_gru keeps state: its stop of the schedule must write its cache entry")
+        T, dev, k = ctx.batch.n_tokens, residual.device, ctx.kernels
+        proj = torch.empty((T, 3 * self.C), dtype=self.dtype, device=dev)
+        k.linear(x, self.w_in, proj)
+        y = torch.empty((T, self.C), dtype=self.dtype, device=dev)
+        k.mingru_scan(proj, self.z_bias, self.x_bias, ctx.cache.state(cache_id), ctx.batch, y, self.C, self.out_scale)
         k.linear(y, self.w_o, residual, accumulate=True)

@@ -22,6 +22,8 @@ def scaled_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
         return inv
     if scaling.get("kind") == "yarn":
         return yarn_inverse_frequencies(rotary_dim, float(theta), scaling, inv)
+    if scaling.get("kind") == "linear":           # every frequency divided by the factor (positions stretched)
+        return inv / float(scaling["factor"])
     factor = float(scaling["factor"])
     low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
     old = float(scaling["original_max_position_embeddings"])
@@ -60,8 +62,9 @@ def table_gain(scaling: Optional[dict]) -> float:
 
 @register_position_encoding("rotary")
 class Rotary:
-    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling`` (None, the llama3 keys, or
-    ``{"kind": "yarn", "factor", "original", "fast", "slow"}``, which also scales the tables), ``pairing``
+    """params: ``head_dim``, ``rotary_dim``, ``theta``, ``max_positions``, ``scaling`` (None, the llama3 keys,
+    ``{"kind": "linear", "factor"}``, or ``{"kind": "yarn", "factor", "original", "fast", "slow"}``, which also
+    scales the tables), ``pairing``
     (``"halves"``: coordinate i turns with i + rotary_dim/2, the default; ``"interleaved"``: 2i with 2i + 1).
 
     Interface of a position encoding: ``encode_and_append(ctx, qkv, kv, n_q, n_kv, write)``
