@@ -1,0 +1,384 @@
+"""The Ronelorn design in the engine against the plain statement of it (``plain_ronelorn``): every mixer alone
+through a cache of its own, the kernels against one another, then whole models through the step function in
+every way of cutting and batching, and generation through the entry point."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ronelorn as pr
+import tiny_ronelorn as tr
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def make_model(cfg, store, dtype, max_tokens=2048, **kw):
+    from supersonic_b200.engine import Model
+    return Model.from_config(cfg, store, dtype=dtype, device=DEV, max_tokens=max_tokens, **kw)
+
+
+def run_in_portions(model, tokens, cuts):
+    """Logits of every position [T, vocab] with the sequence fed in portions of the given sizes."""
+    from supersonic_b200.engine import StepEntry
+    slot, at, rows = model.open_sequence(), 0, []
+    for n in cuts:
+        rows.append(model.step([StepEntry(slot, tokens[at:at + n], list(range(n)))]).cpu())
+        at += n
+    assert at == len(tokens)
+    model.close_sequence(slot)
+    model.check_errors()
+    return torch.cat(rows).double()
+
+
+def position_errors(got, ref):
+    return (got - ref).pow(2).mean(-1).sqrt() / ref.std(-1).clamp_min(1e-6)
+
+
+def close(got, ref, dtype, what=""):
+    """float32: a few units of float32 rounding of the logits' size.  bfloat16: the error's root mean square per
+    position against the spread of that position's logits: the typical position, how many are far off, and the
+    worst one.  The float32 runs of the same tests are the sharp ones."""
+    assert torch.isfinite(got).all(), what
+    if dtype == torch.float32:
+        assert float((got - ref).abs().max()) < 2e-4 * max(1.0, float(ref.abs().max())), what
+    else:
+        rel = position_errors(got, ref)
+        assert float(rel.median()) < 0.05 and float((rel > 0.08).double().mean()) <= 0.1 and float(rel.max()) < 0.4, \
+            (what, rel.median(), (rel > 0.08).double().mean(), rel.max())
+
+
+def tokens_of(cfg, n, seed):
+    return np.random.default_rng(seed).integers(0, cfg.vocab, n).tolist()
+
+
+def reference(cfg, plain, tokens):
+    return pr.forward(tokens, plain, cfg.to_dict())[0]
+
+
+# ---- the parts alone ---------------------------------------------------------------------------------
+def part_context(dtype, store, max_positions=600):
+    from supersonic_b200.csrc.kernel_sets import kernel_set_for
+    from supersonic_b200.parts import BuildContext, WeightAccess
+    return BuildContext(torch.device(DEV), dtype, kernel_set_for(dtype), WeightAccess(store, DEV), max_positions)
+
+
+def step_context(build, cache, entries):
+    from supersonic_b200.engine import StepContext, pack_step
+    starts = [cache.length(e.slot) for e in entries]
+    batch = pack_step(entries, starts, DEV)
+    for e in entries:
+        cache.reserve(e.slot, len(e.tokens))
+    cache.sync()
+    return StepContext(batch, cache, build.kernels, build.dtype)
+
+
+def mixer_alone(spec, position, store, dtype, x, pieces):
+    """What the mixer adds into a zeroed stream for one sequence whose rows ``x`` arrive in pieces, through a cache
+    of its own that holds the mixer's need under id 0."""
+    from supersonic_b200.cache import SequenceCache
+    from supersonic_b200.engine import StepEntry
+    from supersonic_b200.parts import MIXERS, POSITION_ENCODINGS
+    build = part_context(dtype, store)
+    mixer = MIXERS[spec.kind](spec.params, spec.weights, build)
+    pos = None if position is None else POSITION_ENCODINGS[position.kind](position.params, {}, build)
+    cache = SequenceCache({0: mixer.cache_need()}, 1024, 1024, dtype, DEV)
+    slot, at, out = cache.acquire(), 0, []
+    for n in pieces:
+        ctx = step_context(build, cache, [StepEntry(slot, [0] * n)])
+        res = torch.zeros(n, x.shape[1], device=DEV)
+        mixer.forward(ctx, x[at:at + n].to(DEV, dtype), res, 0, True, pos)
+        cache.advance(slot, n)
+        out.append(res.cpu())
+        at += n
+    cache.check()
+    return torch.cat(out).double()
+
+
+PIECES = [70, 2, 2, 59] + [1] * 17 + [90, 1, 1, 1, 2]      # crosses page borders; portions of two; token by token
+T_ALONE = sum(PIECES)
+
+
+def rows_for(cfg, seed, dtype):
+    return torch.randn(T_ALONE, cfg.width, generator=torch.Generator().manual_seed(seed)).to(dtype)
+
+
+def tolerance(dtype, ref, loose=0.04):
+    return (1e-4 if dtype == torch.float32 else loose) * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 0), ("B", 1), ("C", 0), ("C", 3), ("D", 0), ("D", 3)])
+def test_window_attention_with_pooled_runs_alone(dtype, name, layer):
+    """Windows of 5 to 100 tokens and runs of 3 to 16 against pages of 64: a prompt that crosses window, run and
+    page borders, then portions of two and single tokens; values turned and turned back; capped and uncapped."""
+    cfg, store, plain = tr.build(name)
+    block = cfg.build_spec().blocks[layer]
+    x = rows_for(cfg, layer, dtype)
+    ref = cfg.residual_mult * pr.attention(x.double(), plain, f"l{layer}.mix", cfg.layers[layer]["mixer"], cfg.norm_eps)
+    got = mixer_alone(block.mixer, block.position, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 2), ("B", 0), ("C", 1), ("D", 1), ("D", 4)])
+def test_window_attention_with_kept_tokens_and_sink_alone(dtype, name, layer):
+    """One to seventy kept tokens, windows of one to 130 tokens; the norm over the whole projection."""
+    cfg, store, plain = tr.build(name)
+    block = cfg.build_spec().blocks[layer]
+    x = rows_for(cfg, 10 + layer, dtype)
+    ref = cfg.residual_mult * pr.attention_2(x.double(), plain, f"l{layer}.mix", cfg.layers[layer]["mixer"], cfg.norm_eps)
+    got = mixer_alone(block.mixer, block.position, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,layer", [("A", 1), ("A", 4), ("B", 2), ("C", 2), ("D", 2)])
+def test_min_gru_alone(dtype, name, layer):
+    cfg, store, plain = tr.build(name)
+    block = cfg.build_spec().blocks[layer if name != "A" or layer < 3 else 3]     # A's entry 3 has no block of its own
+    x = rows_for(cfg, 20 + layer, dtype)
+    ref = cfg.residual_mult * pr.min_gru(x.double(), plain, f"l{layer}.mix", cfg.layers[layer]["mixer"])
+    got = mixer_alone(block.mixer, None, store, dtype, x, PIECES)
+    assert float((got - ref).abs().max()) < tolerance(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_dense_feed_forward_norm_and_embedding_alone(dtype):
+    from supersonic_b200.parts import EMBEDDINGS, FEED_FORWARDS, NORMS
+    from supersonic_b200.engine import StepEntry
+    from supersonic_b200.cache import SequenceCache, StateNeed
+    cfg, store, plain = tr.build("A")
+    spec = cfg.build_spec()
+    build = part_context(dtype, store)
+    cache = SequenceCache({0: StateNeed(1)}, 256, 256, dtype, DEV)
+    tokens = tokens_of(cfg, 37, 1)
+    ctx = step_context(build, cache, [StepEntry(cache.acquire(), tokens)])
+    emb = EMBEDDINGS[spec.embedding.kind](spec.embedding.params, spec.embedding.weights, build)
+    x = emb(ctx, ctx.batch.token_ids)
+    want = plain["embed"].double()[torch.tensor(tokens)] * cfg.embedding_scale
+    assert x.dtype == torch.float32 and float((x.cpu().double() - want).abs().max()) < 1e-5 * float(want.abs().max())
+    block = spec.blocks[0]
+    norm = NORMS[block.feed_forward_norm.kind](block.feed_forward_norm.params, block.feed_forward_norm.weights, build)
+    ff = FEED_FORWARDS[block.feed_forward.kind](block.feed_forward.params, block.feed_forward.weights, build)
+    rows = torch.randn(37, cfg.width, generator=torch.Generator().manual_seed(5)) * 3.0
+    normed = norm(ctx, rows.to(DEV))
+    assert normed.dtype == dtype
+    ref_n = pr.block_norm(rows.double(), plain, "l0.norm2", cfg.norm_eps)
+    assert float((normed.cpu().double() - ref_n).abs().max()) < tolerance(dtype, ref_n, 0.01)
+    res = torch.zeros(37, cfg.width, device=DEV)
+    ff.forward(ctx, normed, res)
+    ref = cfg.residual_mult * pr.dense(normed.cpu().double(), plain, "l0.mlp")
+    assert float((res.cpu().double() - ref).abs().max()) < tolerance(dtype, ref, 0.02)
+
+
+# ---- whole models through the step function --------------------------------------------------------
+def test_stream_after_every_layer():
+    """float32: the stream after every layer (one that runs with another's tensors counts as a layer of its own),
+    and the logits, against the plain statement."""
+    from supersonic_b200.engine import StepEntry
+    for name in ("A", "B", "C", "D"):
+        cfg, store, plain = tr.build(name)
+        model = make_model(cfg, store, torch.float32)
+        tokens = tokens_of(cfg, 90, 3)
+        ref, streams = pr.forward(tokens, plain, cfg.to_dict())
+        seen = []
+        model.layer_probe = lambda stop, x: seen.append(x.cpu().double())
+        slot = model.open_sequence()
+        got = model.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().double()
+        assert len(seen) == len(streams) == len(cfg.layers)
+        for i, s in enumerate(seen):
+            assert float((s - streams[i]).abs().max()) < 1e-4 * max(1.0, float(streams[i].abs().max())), (name, i)
+        close(got, ref, torch.float32, name)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_of_every_size_and_token_by_token(dtype, name):
+    cfg, store, plain = tr.build(name)
+    model = make_model(cfg, store, dtype)
+    T = 150
+    tokens = tokens_of(cfg, T, 5)
+    ref = reference(cfg, plain, tokens)
+    for cuts in ([T], [64, 64, 22], [63, 2, 2, 61, 3, 7, 2, 10], [1] * 6 + [2] * 3 + [138], [100] + [1] * 50, [1] * T):
+        close(run_in_portions(model, tokens, cuts), ref, dtype, (name, cuts))
+    assert model.cache.slots.n_held == 0
+    model.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_sizes_that_no_fast_kernel_takes_and_sizes_that_all_take(dtype, name):
+    """Odd widths and head sizes (every operation on its plain kernel, also in bfloat16) and round ones: a prompt
+    in portions, then decoding, in a batch of two."""
+    from supersonic_b200.engine import StepEntry
+    cfg, store, plain = tr.build(name)
+    model = make_model(cfg, store, dtype)
+    seqs = [tokens_of(cfg, 230, 31), tokens_of(cfg, 150, 32)]
+    refs = [reference(cfg, plain, q) for q in seqs]
+    slots = [model.open_sequence() for _ in seqs]
+    got = [[], []]
+    plan = [((0, 180), (0, 146)), ((180, 210), (146, 148))] + \
+           [((210 + i, 211 + i), (148 + i, 149 + i) if i < 2 else None) for i in range(20)]
+    for step in plan:
+        entries = [StepEntry(slots[i], seqs[i][lo_hi[0]:lo_hi[1]], list(range(lo_hi[1] - lo_hi[0])))
+                   for i, lo_hi in enumerate(step) if lo_hi]
+        rows = model.step(entries).cpu().double()
+        at = 0
+        for i, lo_hi in enumerate(step):
+            if lo_hi:
+                got[i].append(rows[at:at + lo_hi[1] - lo_hi[0]])
+                at += lo_hi[1] - lo_hi[0]
+    close(torch.cat(got[0]), refs[0], dtype, name)
+    close(torch.cat(got[1]), refs[1], dtype, name)
+    model.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_unequal_batches_against_each_alone_and_reused_slots(dtype, name):
+    """Requests of 1 to 260 tokens start together and decode together, the short ones ending first; then other
+    requests run in the slots, pages, pooled rows and state rows those gave back."""
+    from supersonic_b200.engine import StepEntry
+    cfg, store, plain = tr.build(name)
+    model = make_model(cfg, store, dtype, max_tokens=1024)
+    for round_, lens in enumerate(([1, 5, 64, 65, 131], [131, 2, 66], [260, 3, 195, 64], [7, 129, 64, 3])):
+        decode = [3, 9, 14, 6, 11][: len(lens)]
+        seqs = [tokens_of(cfg, n + d, 100 * round_ + i) for i, (n, d) in enumerate(zip(lens, decode))]
+        refs = [reference(cfg, plain, s) for s in seqs]
+        slots = [model.open_sequence() for _ in seqs]
+        got = [[] for _ in seqs]
+        rows = model.step([StepEntry(s, q[:n], list(range(n))) for s, q, n in zip(slots, seqs, lens)]).cpu().double()
+        at = 0
+        for i, n in enumerate(lens):
+            got[i].append(rows[at:at + n])
+            at += n
+        for step in range(max(decode)):
+            live = [i for i in range(len(seqs)) if step < decode[i]]
+            rows = model.step([StepEntry(slots[i], [seqs[i][lens[i] + step]], [0]) for i in live]).cpu().double()
+            for r, i in enumerate(live):
+                got[i].append(rows[r:r + 1])
+            for i in live:
+                if step == decode[i] - 1:
+                    model.close_sequence(slots[i])          # its slot, pages and state go back while the others go on
+        for i in range(len(seqs)):
+            close(torch.cat(got[i]), refs[i], dtype, (round_, i))
+        model.check_errors()
+        assert model.cache.slots.n_held == 0
+        model.cache.check()
+
+
+def sharpened(name="A", gate=-5.5, sharp=5.0, sharp_kept=10.0, loud_kept=3.0):
+    """The configuration's weights changed so that faults show.  The weights of the norms of q are scaled up, so
+    that a query's output stands on the few keys whose scores are high: a key, a kept token or a pooled run more
+    or less then moves the logits by far more than any tolerance.  The recurrent layers' update gates are pushed
+    down, so that what the state took in hundreds of tokens back still counts."""
+    cfg, store, plain = tr.build(name)
+    changes = {}
+    for i, l in enumerate(cfg.layers):
+        if l.get("weights_of") is not None:
+            continue
+        if l["type"] == "mingru":
+            changes[f"l{i}.mix.z.b"] = plain[f"l{i}.mix.z.b"].float() + gate
+        elif l["type"] == "attention_2":           # its sink takes weight from every key: sharper still, and louder
+            changes[f"l{i}.mix.q.norm"] = plain[f"l{i}.mix.q.norm"].float() * sharp_kept
+            changes[f"l{i}.mix.o"] = plain[f"l{i}.mix.o"].float() * loud_kept
+        else:
+            changes[f"l{i}.mix.q.norm"] = plain[f"l{i}.mix.q.norm"].float() * sharp
+    store, plain = tr.changed(plain, **{k.replace(".", "__"): v for k, v in changes.items()})
+    return cfg, store, plain
+
+
+def _variant(cfg, layer, **mask):
+    d = copy.deepcopy(cfg.to_dict())
+    for l in d["layers"]:
+        if l is d["layers"][layer] or l.get("weights_of") == layer:
+            l["mixer"]["mask"].update(mask)
+    return d
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edges_kept_tokens_pooled_runs_far_tokens_and_page_borders_show(dtype):
+    cfg, store, plain = sharpened("A")
+    T = 330
+    tokens = tokens_of(cfg, T, 9)
+    ref = reference(cfg, plain, tokens)
+    # the test is sharp: a window one token longer, a kept token more, runs of another length (which are seen
+    # earlier or later) each give other logits at most positions behind the first window ...
+    # (one key of a window of 17 beside a sink seldom carries a query, so the second layer's share is smaller)
+    for layer, mask, share in ((0, {"size": 21}, 0.5), (2, {"size": 18}, 0.3), (2, {"keep_first": 4}, 0.2),
+                               (0, {"pool": 5}, 0.5), (0, {"pool": 0}, 0.5)):
+        other = position_errors(pr.forward(tokens, plain, _variant(cfg, layer, **mask))[0], ref)
+        assert float((other[40:] > 0.08).double().mean()) > share and float(other[40:].median()) > 0.03, (layer, mask)
+    # ... and a sequence that has lost what came 200 and more positions before gives other logits at its end
+    tail = position_errors(pr.forward(tokens[200:], plain, cfg.to_dict())[0], ref[200:])
+    assert float(tail[-30:].min()) > 0.2
+    model = make_model(cfg, store, dtype)
+    # cuts at window edges (17, 20), run ends (4, 8, ...), one before and one behind them, at page borders (64, 128),
+    # the first tokens one by one, and decoding across all of these
+    for cuts in ([T], [1, 1, 1, 1, 12, 1, 1, 1, 1, 1, 1, 1, 18, 1, 1, 19, 1, 63, 1, 1, 200],
+                 [16, 2, 2, 2, 19, 2, 21, 64] + [1] * 202, [256] + [1] * 74, [2] * 165):
+        close(run_in_portions(model, tokens, cuts), ref, dtype, cuts)
+
+
+def test_long_decoding_keeps_every_state():
+    """400 tokens decoded one by one after a prompt of two, in float32 and with slow gates: the recurrent state, the
+    kept tokens' pages and the pooled rows are carried over hundreds of steps and several pages."""
+    cfg, store, plain = sharpened("B")
+    model = make_model(cfg, store, torch.float32)
+    tokens = tokens_of(cfg, 402, 21)
+    close(run_in_portions(model, tokens, [2] + [1] * 400), reference(cfg, plain, tokens), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(dtype):
+    """Prompts of unequal lengths in batches of three through ``Engine.generate`` (its scheduler, cache and
+    sampler): the tokens are those the plain statement picks greedily, and in bfloat16 every picked token
+    is the plain statement's first or close second choice."""
+    from supersonic_b200.api import Engine
+    cfg, store, plain = tr.build("A")
+    model = make_model(cfg, store, dtype, max_tokens=1024, max_seq_tokens=128)
+    prompts = [tokens_of(cfg, n, 40 + n) for n in (1, 9, 64, 17, 70)]
+    out = Engine(model).generate(prompts, max_new_tokens=30, temperature=0.0, ignore_eos=True, batch_size=3)
+    assert [len(o) for o in out] == [30] * len(prompts)
+    for prompt, new in zip(prompts, out):
+        seq = list(prompt)
+        for tok in new:
+            logits = reference(cfg, plain, seq)[-1]
+            if dtype == torch.float32:
+                assert tok == int(logits.argmax())
+            else:
+                assert float(logits.max() - logits[tok]) < 0.05 * float(logits.std())
+            seq.append(tok)
+    assert model.cache.slots.n_held == 0
+
+
+def test_trace_replay_of_a_model_folder(tmp_path):
+    """``bin/trace_run`` on a written folder: a batch of two prompts, decode steps, and a third request in a freed
+    slot, logits against the plain statement."""
+    import json, os, subprocess, sys
+    from supersonic_b200.weights import WeightStore, write_model_folder
+    cfg, _, _ = tr.build("A")
+    folder = write_model_folder(cfg, 3, str(tmp_path / "m"), std=0.3)
+    st = WeightStore.from_dir(folder)
+    plain = {n: st.get(n) for n in st.names()}
+    a, b, c = tokens_of(cfg, 70, 1), tokens_of(cfg, 5, 2), tokens_of(cfg, 9, 3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b[:3], "want": [2]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:67], "want": [0]}, {"id": "b", "tokens": b[3:4], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[67:68], "want": [0]}, {"id": "b", "tokens": b[4:5], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[68:70], "want": [1]}], "end": ["a"]},
+             {"step": 4, "entries": [{"id": "c", "tokens": c, "want": [8]}], "end": ["c"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "256"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    ra, rb, rc = (reference(cfg, plain, s) for s in (a, b, c))
+    want = {0: torch.cat([ra[[0, 65]], rb[[2]]]), 1: ra[[66]], 2: torch.cat([ra[[67]], rb[[4]]]), 3: ra[[69]], 4: rc[[8]]}
+    for i, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, cfg.vocab)).double()
+        close(got, ref, torch.float32, i)
