@@ -162,11 +162,12 @@ class CacheBook:
                  group_pages: Optional[Sequence] = None):
         w = _ints([int(x) if x else 0 for x in windows])
         n = len(windows)
-        keep = _ints([int(x) if x else 0 for x in (keep_first if keep_first is not None else [0] * n)])
-        stride = _ints([int(x) if x else 1 for x in (strides if strides is not None else [1] * n)])
-        pages = _ints([int(x) if x else 0 for x in (group_pages if group_pages is not None else [0] * n)])
-        if len(keep) != n or len(stride) != n or len(pages) != n:
+        per_group = [list(x) if x is not None else [d] * n for x, d in ((keep_first, 0), (strides, 1), (group_pages, 0))]
+        if any(len(x) != n for x in per_group):
             raise CacheError("one kept-rows figure, stride and page count per group")
+        keep = _ints([int(x) if x else 0 for x in per_group[0]])
+        stride = _ints([int(x) if x else 1 for x in per_group[1]])
+        pages = _ints([int(x) if x else 0 for x in per_group[2]])
         h = lib().ssb_cache_book_new_groups(n, w, keep, stride, pages, n_pages, pages_per_seq, max_slots, max_seq_tokens)
         if not h:
             raise CacheError("the cache needs at least one page, one slot and room for one token")

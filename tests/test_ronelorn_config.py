@@ -114,3 +114,15 @@ def test_the_plain_statements_masks():
     # runs of 3 before a window of 4: run 0 (tokens 0..2) is seen from position 6 on, run 1 from 9 on
     assert pr.runs_seen(5, 4, 3) == [] and pr.runs_seen(6, 4, 3) == [0] and pr.runs_seen(8, 4, 3) == [0]
     assert pr.runs_seen(9, 4, 3) == [0, 1] and pr.runs_seen(100, 4, 0) == []
+
+
+def test_a_cache_of_recurrent_state_alone():
+    """A model of recurrent layers only has no key store at all."""
+    from supersonic_b200.cache import SequenceCache, StateNeed
+    cache = SequenceCache({0: StateNeed(4), 1: StateNeed(7)}, 256, 256, torch.float32, "cpu")
+    slot = cache.acquire()
+    cache.reserve(slot, 5)
+    cache.advance(slot, 5)
+    assert cache.length(slot) == 5 and cache.state(1).shape[1] == 7
+    cache.check()
+    cache.release(slot)

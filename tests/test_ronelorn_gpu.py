@@ -318,7 +318,7 @@ def test_window_edges_kept_tokens_pooled_runs_far_tokens_and_page_borders_show(d
     model = make_model(cfg, store, dtype)
     # cuts at window edges (17, 20), run ends (4, 8, ...), one before and one behind them, at page borders (64, 128),
     # the first tokens one by one, and decoding across all of these
-    for cuts in ([T], [1, 1, 1, 1, 12, 1, 1, 1, 1, 1, 1, 1, 18, 1, 1, 19, 1, 63, 1, 1, 200],
+    for cuts in ([T], [1, 1, 1, 1, 12, 1, 1, 1, 1, 1, 1, 1, 18, 1, 1, 19, 1, 63, 1, 1, 202],
                  [16, 2, 2, 2, 19, 2, 21, 64] + [1] * 202, [256] + [1] * 74, [2] * 165):
         close(run_in_portions(model, tokens, cuts), ref, dtype, cuts)
 
