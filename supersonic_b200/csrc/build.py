@@ -50,6 +50,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "sequence_ops": {"sources": ["sequence_ops.cu"], "flags": [], "link": []},
     "gated_attention": {"sources": ["gated_attention.cu"], "flags": [], "link": []},
     "window_attention": {"sources": ["window_attention.cu"], "flags": [], "link": []},
+    "window_attention_mma": {"sources": ["window_attention_mma.cu"], "flags": [], "link": []},
     "mingru_ops": {"sources": ["mingru_ops.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
     # the host side's native core: no CUDA in it, so it is compiled by the C++ compiler alone

@@ -378,6 +378,23 @@ class FastKernels(PlainKernels):
             super().sigmoid_attention(q, k_cache, v_cache, batch, page_table, bias, out, n_q, n_kv, dim, vdim, page_shift,
                                       chunk, window, scale)
 
+    def window_attention(self, q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool,
+                         scale, softcap, sinks, value_position, out_scale=1.0):
+        k_cache, v_cache, table, _ = kv
+        pooled = None if pooled_kv is None else pooled_kv[:3]
+        if not ops.window_attention_mma_ok(q, k_cache, v_cache, pooled, out, dim, vdim, page_shift):
+            super().window_attention(q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first,
+                                     pool, scale, softcap, sinks, value_position, out_scale)
+            return
+        vcos = vsin = None
+        v_inter = False
+        if value_position is not None:
+            vcos, vsin, _ = value_position.rotary_tables()
+            v_inter = bool(getattr(value_position, "interleaved", False))
+        ops.window_attention_mma(q, k_cache, v_cache, table, pooled, batch.cu_new, batch.seq_start, batch.seq_slot, out,
+                                 batch.max_new, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool, scale, softcap,
+                                 sinks, vcos, vsin, v_inter, out_scale, pdl=self._chain(batch.n_tokens))
+
     def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
                           dim, vdim):
         chunk, n_sums, n_decays = ops.scan_chunking(batch.n_seqs, batch.max_new, n_heads, dim, vdim)

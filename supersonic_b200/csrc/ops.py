@@ -1022,6 +1022,49 @@ def window_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         _stream()), "window_attention_plain")
 
 
+def window_attention_mma_ok(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pooled, out: torch.Tensor,
+                            dim: int, vdim: int, page_shift: int) -> bool:
+    ok = (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16
+          and out.dtype == torch.bfloat16 and dim % 8 == 0 and vdim % 8 == 0 and 0 < dim <= 128 and 0 < vdim <= 128
+          and page_shift == 6 and q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0
+          and out.data_ptr() % 4 == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and k_cache.data_ptr() % 16 == 0 and v_cache.data_ptr() % 16 == 0)
+    if ok and pooled is not None:
+        ok = all(t.dtype == torch.bfloat16 and t.is_contiguous() and t.data_ptr() % 16 == 0 for t in pooled[:2])
+    return ok
+
+
+def window_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, pooled,
+                         cu_new: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor,
+                         max_new: int, n_q: int, n_kv: int, dim: int, vdim: int, page_shift: int, window: Optional[int],
+                         keep_first: int, pool: int, scale: float, softcap: Optional[float], sinks,
+                         v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_interleaved: bool,
+                         out_scale: float = 1.0, split: Optional[bool] = None, pdl: bool = False) -> None:
+    """``window_attention_plain`` on mma.sync for bfloat16: a block streams what a tile of (token, head of one kv
+    group) rows can see once (pooled rows, kept first tokens, the window's pages); scores, weights and sums
+    float32, the weights entering the second product as hi + lo bfloat16.  ``split`` (default: steps of one
+    token a sequence): 16 rows a block, the warps share a page's keys."""
+    if not window_attention_mma_ok(q, k_cache, v_cache, pooled if pool else None, out, dim, vdim, page_shift):
+        raise KernelError(f"window_attention_mma: dim {dim}, vdim {vdim} or operands not supported")
+    pk, pv, ptable, positions = _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim,
+                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention_mma")
+    _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+    B = seq_slot.shape[0]
+    if cu_new.shape[0] != B + 1 or seq_start.shape[0] != B:
+        raise KernelError("window_attention_mma: one start and slot per sequence, and one more row offset")
+    if split is None:
+        split = max_new * (n_q // n_kv) <= 16
+    _check(_fn("window_attention_mma", "ssb_window_attention_mma")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), c_int(page_table.shape[1]), _ptr(pk),
+        _ptr(pv), _ptr(ptable), c_int(ptable.shape[1] if ptable is not None else 0), _ptr(cu_new), _ptr(seq_start),
+        _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(max_new), c_int(n_q), c_int(n_kv), c_int(dim),
+        c_int(vdim), c_int(page_shift), c_int(int(window) if window else 0), c_int(int(keep_first or 0)),
+        c_int(int(pool or 0)), c_float(scale), c_float(float(softcap) if softcap else 0.0),
+        _ptr(None if (sinks is None or isinstance(sinks, bool)) else sinks), c_int(1 if sinks is True else 0), _ptr(v_cos),
+        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(1 if split else 0),
+        c_int(1 if pdl else 0), _stream()), "window_attention_mma")
+
+
 # ---- minGRU --------------------------------------------------------------------------------
 MINGRU_TILED_MIN_NEW = 64
 

@@ -122,6 +122,52 @@ def test_window_attention_with_pooled_runs_alone(dtype, name, layer):
     assert float((got - ref).abs().max()) < tolerance(dtype, ref)
 
 
+@pytest.mark.parametrize("dim,vdim,heads,kv_heads,window,keep,pool,cap,sink,turn", [
+    (64, 64, 8, 2, 45, 0, 4, 20.0, None, "halves"), (128, 128, 4, 1, 70, 0, 3, None, None, "interleaved"),
+    (32, 48, 6, 6, 20, 5, 0, None, True, None), (80, 128, 16, 1, 64, 70, 0, 8.0, "each", None),
+    (128, 64, 3, 3, 129, 2, 7, None, True, "halves"), (24, 8, 40, 2, 33, 0, 0, None, None, None),
+    (64, 64, 4, 2, None, 0, 0, 15.0, True, "interleaved")])
+def test_window_attention_kernels_agree(dim, vdim, heads, kv_heads, window, keep, pool, cap, sink, turn):
+    """The tensor-core kernel against the plain one in bfloat16, for head sizes that fill its tiles and for ones
+    that it pads: three sequences of unequal lengths as prompts that continue a cache, and as decode steps, with
+    pages in a shuffled order and a pooled store of its own; the two differ by the rounding of the output alone."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(dim + vdim)
+    lens, new = [330, 64, 131], [170, 64, 1]
+    pages_per, B = 6, 3
+    kc = (torch.randn(B * pages_per + 1, kv_heads, 64, dim, device=DEV, generator=g) * 0.6).bfloat16()
+    vc = (torch.randn(B * pages_per + 1, kv_heads, 64, vdim, device=DEV, generator=g) * 0.6).bfloat16()
+    table = (torch.randperm(B * pages_per, device=DEV, generator=g).int() + 1).view(B, pages_per).contiguous()
+    pooled = None
+    if pool:
+        pk = (torch.randn(B * 2 + 1, kv_heads, 64, dim, device=DEV, generator=g) * 0.6).bfloat16()
+        pv = (torch.randn(B * 2 + 1, kv_heads, 64, vdim, device=DEV, generator=g) * 0.6).bfloat16()
+        pooled = (pk, pv, (torch.randperm(B * 2, device=DEV, generator=g).int() + 1).view(B, 2).contiguous())
+    sinks = (torch.randn(heads, device=DEV, generator=g) + 1.0) if sink == "each" else sink
+    vcos = vsin = None
+    if turn:
+        angle = torch.arange(400, device=DEV).float()[:, None] * (50.0 ** (-torch.arange(vdim // 2, device=DEV).float() * 2 / vdim))
+        vcos, vsin = angle.cos().contiguous(), angle.sin().contiguous()
+    for counts in (new, [1, 1, 1]):
+        T = sum(counts)
+        q = (torch.randn(T, heads * dim + 8, device=DEV, generator=g) * 0.6).bfloat16()[:, :heads * dim]
+        pos = torch.cat([torch.arange(n - c, n) for n, c in zip(lens, counts)]).int().to(DEV)
+        slot = torch.cat([torch.full((c,), i) for i, c in enumerate(counts)]).int().to(DEV)
+        cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+        start = torch.tensor([n - c for n, c in zip(lens, counts)], dtype=torch.int32, device=DEV)
+        seq_slot = torch.arange(B, dtype=torch.int32, device=DEV)
+        want = torch.empty(T, heads * vdim, device=DEV, dtype=torch.bfloat16)
+        ops.window_attention_plain(q, kc, vc, table, pooled, pos, slot, want, heads, kv_heads, dim, vdim, 6, window, keep, pool,
+                                   dim ** -0.5, cap, sinks, vcos, vsin, turn == "interleaved", 0.5)
+        for split in (None, True, False):
+            got = torch.zeros_like(want)
+            ops.window_attention_mma(q, kc, vc, table, pooled, cu, start, seq_slot, got, max(counts), heads, kv_heads, dim, vdim,
+                                     6, window, keep, pool, dim ** -0.5, cap, sinks, vcos, vsin, turn == "interleaved", 0.5,
+                                     split=split)
+            err = float((got.float() - want.float()).abs().max())
+            assert err < 0.01 * max(1.0, float(want.float().abs().max())), (counts, split, err)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,layer", [("A", 2), ("B", 0), ("C", 1), ("D", 1), ("D", 4)])
 def test_window_attention_with_kept_tokens_and_sink_alone(dtype, name, layer):
