@@ -335,6 +335,35 @@ def _vufadra_sizes(name):
     return vuf, lla
 
 
+def _ronelorn_sizes(name):
+    """(Ronelorn config.json, the Vufadra configuration of the same width, layer count, feed-forward and vocabulary:
+    the closest existing design, with chunked attention over separate key and value widths, an element-wise gated
+    recurrence and the dense feed-forward).  One layer of each mixer plus a second window layer that runs with the
+    first one's weights on a cache of its own."""
+    def pooled(heads, kv, dim, window, pool):
+        return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                "softcap": 30.0, "mask": {"size": window, "pool": pool},
+                "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 2.0}}}}
+
+    def kept(heads, kv, dim, window, keep):
+        return {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                "mask": {"size": window, "keep_first": keep}, "rot": {"base": 10000.0, "dims": dim // 2}}}
+
+    def mingru(width):
+        return {"type": "mingru", "mixer": {"width": width}}
+    vuf, lla = _vufadra_sizes(name)
+    width, ff = vuf["width"], vuf["layers"][0]["mlp"]["ff"]
+    if name == "2048":
+        mixers = [pooled(16, 4, 128, 512, 16), kept(32, 8, 64, 512, 4), mingru(2048), None]
+    else:
+        mixers = [pooled(8, 2, 128, 256, 16), kept(16, 4, 64, 256, 4), mingru(1024), None]
+    layers = [dict(m, mlp={"kind": "dense", "ff": ff}) for m in mixers[:3]]
+    layers.append(dict(layers[0], weights_of=0))
+    ron = {"architecture": "Ronelorn", "vocab": vuf["vocab"], "width": width, "norm": {"eps": 1e-5},
+           "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.5, "layers": layers}
+    return ron, vuf
+
+
 def _operation_work(model, tokens):
     """Algorithmic work of one prompt of ``tokens`` tokens per operation of the model's parts: (FLOPs, bytes).
     Matrix products count 2 per multiply-add; attention counts its scores and weighted sums over the causal
@@ -345,7 +374,8 @@ def _operation_work(model, tokens):
         f, b = work.get(name, (0, 0))
         work[name] = (f + flops, b + nbytes)
     T, causal = tokens, tokens * (tokens + 1) // 2
-    for b in model.blocks:
+    # a block runs once per stop of the schedule: a layer that runs with another's weights is a second stop there
+    for b in [model.blocks[stop.layer] for stop in model.spec.schedule]:
         m, ff = b.mixer, b.feed_forward
         kind = type(m).__name__
         if kind == "LatentAttention":
@@ -379,6 +409,16 @@ def _operation_work(model, tokens):
                     HD = half.H * half.dim
                     add("mixer.linear", 2 * T * (sum(w.numel() for w in half.w) + half.w2.numel() + half.w_o.numel()))
                     add("mixer.matrix_state_scan", 6 * T * HD * half.dim, T * HD * (3 * 2 + 4 + 4))
+        elif kind == "WindowAttention":
+            add("mixer.linear", 2 * T * (m.w_qkv.numel() + m.w_o.numel()))
+            w = int(m.window or T)
+            pairs = sum(min(i + 1, w) + (max(0, i - w + 1) // m.pool if m.pool else min(m.keep_first, max(0, i - w + 1)))
+                        for i in range(T))
+            add("mixer.window_attention", 2 * pairs * m.n_q * (m.dim + m.vdim))
+            add("mixer.qkv_prepare", 0, T * (m.n_q * m.dim * 4 + m.n_kv * (m.dim + m.vdim) * 4))
+        elif kind == "MinGRU":
+            add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_o.numel()))
+            add("mixer.mingru_scan", 10 * T * m.C, T * m.C * (3 * 2 + 2))                # z, x, g in; the gated state out
         elif kind == "Attention":
             add("mixer.linear", 2 * T * (m.w_qkv.numel() + m.w_o.numel()))
             add("mixer.project_rope_append", 2 * T * m.w_qkv.numel())
@@ -394,6 +434,9 @@ def _operation_work(model, tokens):
         elif fk == "SwiGLU":
             add("feed_forward.gate_up_swiglu", 2 * T * ff.w_gate_up.numel())
             add("feed_forward.linear", 2 * T * ff.w_down.numel())
+        elif fk == "DenseFeedForward":
+            add("feed_forward.linear_activation", 2 * T * ff.w_up.numel())
+            add("feed_forward.linear", 2 * T * ff.w_down.numel())
     return work
 
 
@@ -406,13 +449,15 @@ def design_comparison(args):
     from supersonic_b200.engine import Model, StepEntry
     from supersonic_b200.weights import RandomWeightStore
     pk, pk_src = peaks()
-    sot, lla = (_vufadra_sizes if args.design == "vufadra" else _sotavik_sizes)(args.design_size)
-    out = {"metric": "design_comparison", "design": args.design, "beside": "llama", "size": args.design_size,
+    sizes = {"vufadra": _vufadra_sizes, "sotavik": _sotavik_sizes, "ronelorn": _ronelorn_sizes}[args.design]
+    sot, lla = sizes(args.design_size)
+    beside = "vufadra" if args.design == "ronelorn" else "llama"
+    out = {"metric": "design_comparison", "design": args.design, "beside": beside, "size": args.design_size,
            "layers": len(sot["layers"]), "dtype": "bf16", "data": "synthetic", "peaks": pk, "peaks_source": pk_src,
            "models": {}}
     clocks = ClockSampler()
     clocks.start()
-    for name, d in ((args.design, sot), ("llama", lla)):
+    for name, d in ((args.design, sot), (beside, lla)):
         cfg = config_from_dict(d)
         store = RandomWeightStore(cfg, seed=3, device="cuda:0", std=0.02, norm_jitter=0.0)
         ctx = max(args.prefill_tokens, args.prompt_len) + 256
@@ -580,7 +625,7 @@ def main():
                     help="also time decode and prompts at further sizes (adds a 'sweep' key to the line)")
     ap.add_argument("--deterministic", action="store_true",
                     help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
-    ap.add_argument("--design", default=None, choices=["sotavik", "vufadra"],
+    ap.add_argument("--design", default=None, choices=["sotavik", "vufadra", "ronelorn"],
                     help="instead of the headline workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="2048", help="width of the compared models: 1024 or 2048")
     args = ap.parse_args()

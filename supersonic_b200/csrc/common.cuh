@@ -33,6 +33,15 @@ template <> __device__ __forceinline__ __nv_bfloat16 ssb_from_float<__nv_bfloat1
     return __float2bfloat16_rn(x);
 }
 
+// An activation between two dense products, in float32.
+//   kind 0: relu(u)^2;  1: gelu with tanh, 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)));  2: silu
+enum { SSB_ACT_RELU_SQUARED = 0, SSB_ACT_GELU_TANH = 1, SSB_ACT_SILU = 2 };
+__device__ __forceinline__ float ssb_activate(float u, int kind) {
+    if (kind == SSB_ACT_RELU_SQUARED) { const float r = fmaxf(u, 0.f); return r * r; }
+    if (kind == SSB_ACT_GELU_TANH) return 0.5f * u * (1.0f + tanhf(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+    return u / (1.0f + expf(-u));
+}
+
 // Location of token `pos` of sequence slot `slot` in a paged cache entry laid out as
 // [page][kv_head][token_in_page][head_dim]; returns the element offset of the head's row.
 __device__ __forceinline__ size_t ssb_cache_row(const int* __restrict__ page_table, int max_pages,

@@ -82,7 +82,7 @@ SSB_API int ssb_rmsnorm_vec(const float* x, const int* rows, const void* w, int 
 // in a scratch that was zero before; this writes them out as bfloat16 and zeroes the scratch for
 // the next projection that uses it.  8 elements a thread.
 __global__ void __launch_bounds__(256)
-round_and_clear_kernel(float* __restrict__ sums, bf16* __restrict__ out, int ldo, int n_rows, int n_cols) {
+round_and_clear_kernel(float* __restrict__ sums, bf16* __restrict__ out, int ldo, int n_rows, int n_cols, int act, float scale) {
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
     const int per_row = n_cols / 8;
@@ -90,9 +90,15 @@ round_and_clear_kernel(float* __restrict__ sums, bf16* __restrict__ out, int ldo
     if (i >= (long long)n_rows * per_row) return;
     const int r = (int)(i / per_row), c = (int)(i % per_row) * 8;
     float4* src = reinterpret_cast<float4*>(sums + (size_t)r * n_cols + c);
-    const float4 a = src[0], b = src[1];
+    float4 a = src[0], b = src[1];
     src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
     src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (act >= 0) {                                         // an activation on the float32 sums, before their one rounding
+        a = make_float4(ssb_activate(a.x, act) * scale, ssb_activate(a.y, act) * scale, ssb_activate(a.z, act) * scale,
+                        ssb_activate(a.w, act) * scale);
+        b = make_float4(ssb_activate(b.x, act) * scale, ssb_activate(b.y, act) * scale, ssb_activate(b.z, act) * scale,
+                        ssb_activate(b.w, act) * scale);
+    }
     __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
     __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
     uint4 v;
@@ -102,13 +108,19 @@ round_and_clear_kernel(float* __restrict__ sums, bf16* __restrict__ out, int ldo
 }
 
 // sums: float32 [n_rows, n_cols] contiguous (left zero); out: bfloat16 [n_rows, n_cols], row stride ldo.
-SSB_API int ssb_round_and_clear(float* sums, void* out, int ldo, int n_rows, int n_cols, int pdl, cudaStream_t stream) {
+// act: -1 none, else out = activation(sums) * scale (kinds of ssb_activate).
+SSB_API int ssb_round_act_clear(float* sums, void* out, int ldo, int n_rows, int n_cols, int act, float scale, int pdl,
+                                cudaStream_t stream) {
     if (n_rows <= 0 || n_cols <= 0) return 0;
-    if (n_cols % 8 || ldo % 8 || (((uintptr_t)sums | (uintptr_t)out) & 15)) return SSB_ERR_BAD_SIZE;
+    if (n_cols % 8 || ldo % 8 || (((uintptr_t)sums | (uintptr_t)out) & 15) || act < -1 || act > SSB_ACT_SILU) return SSB_ERR_BAD_SIZE;
     const long long n = (long long)n_rows * (n_cols / 8);
     const int rc = ssb_launch(round_and_clear_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, pdl != 0,
-                              sums, (bf16*)out, ldo, n_rows, n_cols);
+                              sums, (bf16*)out, ldo, n_rows, n_cols, act, scale);
     return rc ? rc : ssb_launch_status();
+}
+
+SSB_API int ssb_round_and_clear(float* sums, void* out, int ldo, int n_rows, int n_cols, int pdl, cudaStream_t stream) {
+    return ssb_round_act_clear(sums, out, ldo, n_rows, n_cols, -1, 1.0f, pdl, stream);
 }
 
 // ---- rope + append: one block per token ------------------------------------------------------

@@ -126,6 +126,36 @@ class FastKernels(PlainKernels):
                 return
         ops.gemm_nt_plain(x, weight, out, accumulate)
 
+    def linear_activation(self, x, weight, out, kind, scale=1.0):
+        """The activation where the product finishes its float32 sums: in the tcgen05 GEMM's epilogue, or, where K
+        is split over blocks that add into a scratch, in the pass that rounds the scratch."""
+        rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
+        xt = as_tensor(x)
+        n, k = weight.shape
+        if not (out.dtype == torch.bfloat16 and ops.gemm_tc_ok(xt, weight, out) and n % 8 == 0 and out.stride(0) % 8 == 0):
+            super().linear_activation(xt, weight, out, kind, scale)
+            return
+        if self.deterministic:
+            ops.gemm_tc_act(xt, weight, out, kind, scale,
+                            tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n) else self._tile_n(rows, n))
+        elif rows <= STREAM_ROWS and n < 16384:
+            sums = self._buffer("split_sums", rows * n, torch.float32, out.device, zero=True)[: rows * n].view(rows, n)
+            ops.gemv_tc(xt, weight, sums, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
+            ops.round_and_clear(sums, out, pdl=self.pdl, act=kind, scale=scale)
+        elif rows <= STREAM_ROWS:
+            ops.gemv_tc(xt, weight, out, ops.TC_STORE, pdl=self.pdl)
+            self.activation(out, out, kind, scale)
+        else:
+            tile_n = self._tile_n(rows, n)
+            splits = self._gemm_splits(rows, n, k, tile_n)
+            if splits > 1:
+                sums = self._buffer("split_sums", rows * n, torch.float32, out.device, zero=True)[: rows * n].view(rows, n)
+                ops.gemm_tc(xt, weight, sums, ops.TC_ACCUMULATE, tile_n=tile_n, splits=splits)
+                ops.round_and_clear(sums, out, pdl=self.pdl, act=kind, scale=scale)
+            else:
+                ops.gemm_tc_act(xt, weight, out, kind, scale,
+                                tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n) else tile_n)
+
     @staticmethod
     def _gemm_splits(rows: int, n: int, k: int, tile_n: int, sms: Optional[int] = None) -> int:
         """Parts a tile's K range is cut into so that the work items fill the SMs once (one block

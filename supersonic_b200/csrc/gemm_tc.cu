@@ -42,6 +42,7 @@ struct TcRope {
     const float* cos_t;        // [positions, head_dim / 2]
     const float* sin_t;
     int max_pages, n_q, n_kv, head_dim, page_shift;
+    float act_scale;           // modes TC_ACT + k: what the activation's result is multiplied by
 };
 
 __device__ __forceinline__ void tc_store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
@@ -158,6 +159,11 @@ hi[4 * i4 + e] = a_ * sv + b_ * cv;                                             
                 }
             } else {
                 bf16* dst = (bf16*)C + (size_t)row * ldc + n;
+                if (mode >= TC_ACT) {                     // on the float32 sums, before their one rounding
+    #pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        r[j] = __float_as_uint(ssb_activate(__uint_as_float(r[j]), mode - TC_ACT) * rope.act_scale);
+                }
                 if (n + 32 <= N) {
     #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
@@ -591,6 +597,15 @@ static int gemm_tc_any(const void* A, int lda, const void* W, int ldw, void* C, 
     if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
     if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
     return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
+}
+
+// C (bfloat16) = activation(A W^T) * scale; act: a kind of ssb_activate.
+SSB_API int ssb_gemm_tc_act(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int act,
+                            float scale, int tile_n, int* error_word, cudaStream_t stream) {
+    if (act < 0 || act > SSB_ACT_SILU) return SSB_ERR_BAD_SIZE;
+    TcRope extra{};
+    extra.act_scale = scale;
+    return gemm_tc_any(A, lda, W, ldw, C, ldc, SSB_BF16, M, N, K, TC_ACT + act, tile_n, 1, error_word, extra, stream);
 }
 
 SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,

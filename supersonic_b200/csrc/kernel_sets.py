@@ -275,8 +275,12 @@ class PlainKernels:
                                    v_inter, out_scale, pdl=self._chain(batch.n_tokens))
 
     def mingru_scan(self, proj, z_bias, x_bias, state, batch, out, width, out_scale=1.0):
+        scratch = None
+        if batch.max_new >= ops.MINGRU_CHUNKED_MIN_NEW:      # a prompt: every 64 tokens in a block of their own
+            scratch = self._scan_scratch(ops.mingru_scan_scratch(batch.n_seqs, batch.max_new, width), out.device)
         ops.mingru_scan(proj, z_bias, x_bias, state, batch.cu_new, batch.seq_slot, out, width, out_scale,
-                        tiled=batch.max_new >= ops.MINGRU_TILED_MIN_NEW, pdl=self._chain(batch.n_tokens))
+                        tiled=batch.max_new >= ops.MINGRU_TILED_MIN_NEW, pdl=self._chain(batch.n_tokens),
+                        max_new=batch.max_new, scratch=scratch)
 
     # ---- experts ---------------------------------------------------------------------
     expert_tile_rows = 64

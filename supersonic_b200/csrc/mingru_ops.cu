@@ -10,6 +10,9 @@
 // a tile of 8 x L tokens is spread over the eight warps, each warp composes its L tokens into one pair (A, B) with
 // S_out = A S_in + B, the pairs are folded in order through shared memory, and each warp then walks its tokens
 // again from its true entry state; both forms compute a_t S + b_t with a_t = 1 - z_t, b_t = z_t cand_t.
+// The chunked scan for prompts: the same tile, but every tile of 64 tokens has a block of its own.  A first launch
+// composes each tile into one pair (A, B) and keeps the entering state aside; a second launch folds the pairs of
+// the tiles before its own from that state, walks its tokens, and the last tile's block writes the state back.
 #include "common.cuh"
 #include <math.h>
 
@@ -147,14 +150,153 @@ mingru_scan_tiled_kernel(const P* __restrict__ proj, int ld, const float* __rest
     }
 }
 
+// Chunked scan.  scratch: per sequence max_chunks pairs [A | B] of `width` floats each, then the entering state.
+// PHASE 0 composes, PHASE 1 folds, walks and writes.  FAST: sigmoids from the fast exponential (bfloat16 rows).
+template <bool FAST> __device__ __forceinline__ float mg_sig(float x) {
+    return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
+template <bool FAST> __device__ __forceinline__ void mg_gates_of(float zp, float up, float& a, float& b) {
+    const float z = mg_sig<FAST>(zp);
+    const float cand = up >= 0.f ? up + 0.5f : mg_sig<FAST>(up);
+    a = 1.0f - z;
+    b = z * cand;
+}
+
+template <typename P, typename T, int L, int PHASE, bool FAST>
+__global__ void __launch_bounds__(MG_WARPS * 32)
+mingru_scan_chunked_kernel(const P* __restrict__ proj, int ld, const float* __restrict__ z_bias, const float* __restrict__ x_bias,
+                           float* __restrict__ state, const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                           T* __restrict__ out, int ldo, int width, float out_scale, float* __restrict__ scratch,
+                           int max_chunks) {
+    __shared__ float As[MG_WARPS][MG_CHANNELS], Bs[MG_WARPS][MG_CHANNELS];
+    ssb_pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, chunk = blockIdx.y, b = blockIdx.z;
+    const int c = blockIdx.x * MG_CHANNELS + 2 * lane;
+    const bool live = c < width;                           // width is even: both channels of a lane or neither
+    float bz[2] = {0.f, 0.f}, bu[2] = {0.f, 0.f};
+    if (live) {
+        if (z_bias) { bz[0] = z_bias[c]; bz[1] = z_bias[c + 1]; }
+        if (x_bias) { bu[0] = x_bias[c]; bu[1] = x_bias[c + 1]; }
+    }
+    ssb_pdl_wait();
+    const int slot = seq_slot[b];
+    if (slot < 0) return;
+    const int t0 = cu_new[b], n_new = cu_new[b + 1] - t0;
+    const int n_chunks = (n_new + MG_WARPS * L - 1) / (MG_WARPS * L);
+    if (chunk >= n_chunks) return;
+    float* pairs = scratch + (size_t)b * (2 * max_chunks + 1) * width;
+    float* entering = pairs + (size_t)2 * max_chunks * width;
+    const int first = chunk * MG_WARPS * L + warp * L;
+    float a[L][2], bb[L][2];
+    float A[2] = {1.f, 1.f}, B[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < L; ++i) {
+        a[i][0] = a[i][1] = 1.f;
+        bb[i][0] = bb[i][1] = 0.f;
+        if (live && first + i < n_new) {
+            const P* row = proj + (size_t)(t0 + first + i) * ld;
+            float z0, z1, u0, u1;
+            MgPair<P>::load(row + c, z0, z1);
+            MgPair<P>::load(row + width + c, u0, u1);
+            mg_gates_of<FAST>(z0 + bz[0], u0 + bu[0], a[i][0], bb[i][0]);
+            mg_gates_of<FAST>(z1 + bz[1], u1 + bu[1], a[i][1], bb[i][1]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < L; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            B[e] = fmaf(a[i][e], B[e], bb[i][e]);
+            A[e] *= a[i][e];
+        }
+    As[warp][2 * lane] = A[0]; As[warp][2 * lane + 1] = A[1];
+    Bs[warp][2 * lane] = B[0]; Bs[warp][2 * lane + 1] = B[1];
+    __syncthreads();
+    if (PHASE == 0) {
+        if (warp == 0 && live) {
+            float Ac[2] = {1.f, 1.f}, Bc[2] = {0.f, 0.f};
+#pragma unroll
+            for (int w = 0; w < MG_WARPS; ++w)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    Bc[e] = fmaf(As[w][2 * lane + e], Bc[e], Bs[w][2 * lane + e]);
+                    Ac[e] *= As[w][2 * lane + e];
+                }
+            *reinterpret_cast<float2*>(pairs + (size_t)(2 * chunk) * width + c) = make_float2(Ac[0], Ac[1]);
+            *reinterpret_cast<float2*>(pairs + (size_t)(2 * chunk + 1) * width + c) = make_float2(Bc[0], Bc[1]);
+            if (chunk == 0)
+                *reinterpret_cast<float2*>(entering + c) = *reinterpret_cast<const float2*>(state + (size_t)slot * width + c);
+        }
+        return;
+    }
+    if (!live) return;
+    // the state that enters this tile: the sequence's, through the pairs of the tiles before
+    float S[2];
+    {
+        const float2 s0 = *reinterpret_cast<const float2*>(entering + c);
+        S[0] = s0.x; S[1] = s0.y;
+    }
+    for (int ch = 0; ch < chunk; ++ch) {
+        const float2 Ap = *reinterpret_cast<const float2*>(pairs + (size_t)(2 * ch) * width + c);
+        const float2 Bp = *reinterpret_cast<const float2*>(pairs + (size_t)(2 * ch + 1) * width + c);
+        S[0] = fmaf(Ap.x, S[0], Bp.x);
+        S[1] = fmaf(Ap.y, S[1], Bp.y);
+    }
+    float s[2] = {S[0], S[1]};                             // the state that enters this warp's tokens
+#pragma unroll
+    for (int w = 0; w < MG_WARPS; ++w) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const float next = fmaf(As[w][2 * lane + e], S[e], Bs[w][2 * lane + e]);
+            S[e] = next;
+            if (w < warp) s[e] = next;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < L; ++i) {
+        if (first + i >= n_new) break;
+        s[0] = fmaf(a[i][0], s[0], bb[i][0]);
+        s[1] = fmaf(a[i][1], s[1], bb[i][1]);
+        float g0, g1;
+        MgPair<P>::load(proj + (size_t)(t0 + first + i) * ld + 2 * width + c, g0, g1);
+        MgPair<T>::store(out + (size_t)(t0 + first + i) * ldo + c, s[0] * (g0 * mg_sig<FAST>(g0)) * out_scale,
+                         s[1] * (g1 * mg_sig<FAST>(g1)) * out_scale);
+    }
+    if (chunk == n_chunks - 1 && warp == 0) {
+        state[(size_t)slot * width + c] = S[0];
+        state[(size_t)slot * width + c + 1] = S[1];
+    }
+}
+
 // proj [T, ld] rows [zp | up | gp] of `width` columns each; out [T, ldo]; state [slots, width] float32.
-// tiled: the tiled scan (width, ld and ldo even, rows aligned to a pair of elements); else the walk.
+// tiled 1: the tiled scan (width, ld and ldo even, rows aligned to a pair of elements); 2: the chunked scan (the
+// same, with scratch of ssb_mingru_scan_scratch floats and the longest run, max_new); else the walk.
 SSB_API int ssb_mingru_scan(const void* proj, int ld, int proj_dtype, const float* z_bias, const float* x_bias, float* state,
                             const int* cu_new, const int* seq_slot, void* out, int ldo, int out_dtype, int n_seqs, int width,
-                            float out_scale, int tiled, int pdl, cudaStream_t stream) {
+                            float out_scale, int tiled, float* scratch, int max_new, int pdl, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (width <= 0 || n_seqs > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
+    if (tiled == 2) {
+        if ((width & 1) || (ld & 1) || (ldo & 1) || !scratch || max_new <= 0) return SSB_ERR_BAD_SIZE;
+        const int chunks = (max_new + MG_WARPS * 8 - 1) / (MG_WARPS * 8);
+        if (chunks > 65535) return SSB_ERR_BAD_SIZE;
+        const dim3 grid((width + MG_CHANNELS - 1) / MG_CHANNELS, chunks, n_seqs), block(MG_WARPS * 32);
+#define SSB_MG_CHUNKED(P, T, FAST)                                                                                          \
+    {                                                                                                                       \
+        rc = ssb_launch(mingru_scan_chunked_kernel<P, T, 8, 0, FAST>, grid, block, 0, stream, pdl != 0, (const P*)proj, ld,  \
+                        z_bias, x_bias, state, cu_new, seq_slot, (T*)out, ldo, width, out_scale, scratch, chunks);          \
+        if (!rc)                                                                                                            \
+            rc = ssb_launch(mingru_scan_chunked_kernel<P, T, 8, 1, FAST>, grid, block, 0, stream, false, (const P*)proj, ld, \
+                            z_bias, x_bias, state, cu_new, seq_slot, (T*)out, ldo, width, out_scale, scratch, chunks);      \
+    }
+        if (proj_dtype == SSB_F32 && out_dtype == SSB_F32) SSB_MG_CHUNKED(float, float, false)
+        else if (proj_dtype == SSB_F32 && out_dtype == SSB_BF16) SSB_MG_CHUNKED(float, bf16, false)
+        else if (proj_dtype == SSB_BF16 && out_dtype == SSB_BF16) SSB_MG_CHUNKED(bf16, bf16, true)
+        else return SSB_ERR_BAD_DTYPE;
+#undef SSB_MG_CHUNKED
+        return rc ? rc : ssb_launch_status();
+    }
     if (tiled) {
         if ((width & 1) || (ld & 1) || (ldo & 1)) return SSB_ERR_BAD_SIZE;
         const dim3 grid((width + MG_CHANNELS - 1) / MG_CHANNELS, n_seqs), block(MG_WARPS * 32);

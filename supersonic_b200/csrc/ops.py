@@ -1067,15 +1067,23 @@ def window_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 
 # ---- minGRU --------------------------------------------------------------------------------
 MINGRU_TILED_MIN_NEW = 64
+MINGRU_CHUNKED_MIN_NEW = 256
+MINGRU_CHUNK = 64           # tokens a block of the chunked scan takes
+
+
+def mingru_scan_scratch(n_seqs: int, max_new: int, width: int) -> int:
+    """float32 elements of scratch the chunked scan needs for runs of up to ``max_new`` tokens."""
+    return n_seqs * (2 * (-(-max_new // MINGRU_CHUNK)) + 1) * width
 
 
 def mingru_scan(proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
                 cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, width: int, out_scale: float = 1.0,
-                tiled: bool = False, pdl: bool = False) -> None:
+                tiled: bool = False, pdl: bool = False, max_new: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """Rows of ``proj`` are [zp | up | gp], ``width`` columns each.  Per channel, over every sequence's new tokens
     from and into its row of ``state`` [slots, width] (float32): z = sigmoid(zp + bz), cand = up + bu + 1/2 where
     up + bu >= 0 and sigmoid(up + bu) below, S <- (1 - z) S + z cand, out = out_scale * S * silu(gp).  ``tiled``:
-    the form that spreads a run of tokens over the warps of a block (even width and strides)."""
+    the form that spreads a run of tokens over the warps of a block (even width and strides); with ``scratch``
+    (``mingru_scan_scratch`` floats) and ``max_new``, every 64 tokens of a run get a block of their own."""
     _need(proj, "proj", None, 2); _need(out, "out", None, 2); _need(state, "state", torch.float32, 2)
     _need(cu_new, "cu_new", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
     B = seq_slot.shape[0]
@@ -1089,10 +1097,17 @@ def mingru_scan(proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Opti
                 raise KernelError("mingru_scan: a bias per channel")
     if tiled and (width % 2 or proj.stride(0) % 2 or out.stride(0) % 2 or proj.data_ptr() % 8 or out.data_ptr() % 8):
         tiled = False
+    form = 1 if tiled else 0
+    if tiled and scratch is not None and max_new > 0:
+        _need(scratch, "scratch", torch.float32, 1)
+        if scratch.numel() < mingru_scan_scratch(B, max_new, width) or scratch.data_ptr() % 8:
+            raise KernelError("mingru_scan: scratch is too small")
+        form = 2
     _check(_fn("mingru_ops", "ssb_mingru_scan")(
         _ptr(proj), c_int(proj.stride(0)), c_int(dtype_code(proj.dtype)), _ptr(z_bias), _ptr(x_bias), _ptr(state),
         _ptr(cu_new), _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B), c_int(width),
-        c_float(out_scale), c_int(1 if tiled else 0), c_int(1 if pdl else 0), _stream()), "mingru_scan")
+        c_float(out_scale), c_int(form), _ptr(scratch if form == 2 else None), c_int(max_new), c_int(1 if pdl else 0),
+        _stream()), "mingru_scan")
 
 
 # ---- experts -----------------------------------------------------------------------------
@@ -1548,6 +1563,27 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")
 
 
+def gemm_tc_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str, scale: float = 1.0,
+                tile_n: Optional[int] = None) -> None:
+    """out (bfloat16) = act(a @ w^T) * scale on the tensor cores: the activation (a kind of ``ACTIVATIONS``) is taken
+    on the float32 sums where the product finishes them, before their one rounding."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} is not known (known: {sorted(ACTIVATIONS)})")
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_tc_act: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if tile_n is None:
+        tile_n = 256 if N > 128 else 128
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemm_tc", "ssb_gemm_tc_act")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N),
+        c_int(K), c_int(ACTIVATIONS[kind]), c_float(scale), c_int(tile_n), _ptr(tc_error_word(a.device)), _stream()),
+        "gemm_tc_act")
+
+
 def gemm_tc_rope_append(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor,
                         sin: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, page_table: torch.Tensor,
                         k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
@@ -1730,14 +1766,18 @@ def rmsnorm_vec(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Te
         c_int(x.shape[1]), c_int(1 if pdl else 0), _stream()), "rmsnorm_vec")
 
 
-def round_and_clear(sums: torch.Tensor, out: torch.Tensor, pdl: bool = False) -> None:
-    """out (bfloat16) = sums (float32, contiguous, same shape) rounded; sums is left zero."""
+def round_and_clear(sums: torch.Tensor, out: torch.Tensor, pdl: bool = False, act: Optional[str] = None,
+                    scale: float = 1.0) -> None:
+    """out (bfloat16) = sums (float32, contiguous, same shape) rounded; sums is left zero.  With ``act`` (a kind of
+    ``ACTIVATIONS``): out = act(sums) * scale, taken in float32 before the rounding."""
     _need(sums, "sums", torch.float32, 2); _need(out, "out", torch.bfloat16, 2)
     if sums.shape != out.shape or not sums.is_contiguous() or sums.shape[1] % 8:
         raise KernelError(f"round_and_clear: shapes sums{tuple(sums.shape)} out{tuple(out.shape)}")
-    _check(_fn("elementwise_ops", "ssb_round_and_clear")(
+    if act is not None and act not in ACTIVATIONS:
+        raise KernelError(f"activation {act!r} is not known (known: {sorted(ACTIVATIONS)})")
+    _check(_fn("elementwise_ops", "ssb_round_act_clear")(
         _ptr(sums), _ptr(out), c_int(out.stride(0)), c_int(sums.shape[0]), c_int(sums.shape[1]),
-        c_int(1 if pdl else 0), _stream()), "round_and_clear")
+        c_int(-1 if act is None else ACTIVATIONS[act]), c_float(scale), c_int(1 if pdl else 0), _stream()), "round_and_clear")
 
 
 def rope_append_vec_ok(qkv: torch.Tensor, cos, head_dim: int, rotary_dim: int, write_cache: bool) -> bool:

@@ -445,13 +445,8 @@ SSB_API int ssb_swiglu(const void* gate_up, int ld, void* z, int ldz, int dtype,
 // ---------------------------------------------------------------------------------------
 // An activation between two dense products: z[t, c] = act(u[t, c]) * scale, in float32.
 //   kind 0: relu(u)^2;  1: gelu with tanh, 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3)));  2: silu
+//   (ssb_activate, shared with the kernels that apply it where they finish a product)
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ float ssb_activate(float u, int kind) {
-    if (kind == 0) { const float r = fmaxf(u, 0.f); return r * r; }
-    if (kind == 1) return 0.5f * u * (1.0f + tanhf(0.7978845608028654f * (u + 0.044715f * u * u * u)));
-    return u / (1.0f + expf(-u));
-}
-
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ u, int ld, T* __restrict__ z, int ldz, int width, size_t total,
                                   int kind, float scale) {

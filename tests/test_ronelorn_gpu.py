@@ -192,6 +192,67 @@ def test_min_gru_alone(dtype, name, layer):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [64, 130, 322])
+def test_min_gru_scan_forms_agree(dtype, width):
+    """The walk, the tiled scan and the scan with a block per 64 tokens on the same rows: three sequences of
+    unequal lengths (one of a single token, one that ends inside a tile, one of several tiles and a rest) that
+    continue a state, twice in a row, against the recurrence written out in float64."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(width)
+    counts = [300, 1, 77]
+    T, B = sum(counts), len(counts)
+    cu = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=DEV)
+    bz, bu = torch.randn(width, device=DEV, generator=g), torch.randn(width, device=DEV, generator=g)
+    states = [torch.zeros(3, width, device=DEV) for _ in range(3)]
+    ref_state = torch.zeros(3, width, dtype=torch.float64)
+    for _ in range(2):
+        proj = (torch.randn(T, 3 * width + 8, device=DEV, generator=g) * 2.0).to(dtype)[:, :3 * width]
+        outs = [torch.zeros(T, width, device=DEV, dtype=dtype) for _ in range(3)]
+        scratch = torch.empty(ops.mingru_scan_scratch(B, max(counts), width), device=DEV)
+        ops.mingru_scan(proj, bz, bu, states[0], cu, slots, outs[0], width, 0.7)
+        ops.mingru_scan(proj, bz, bu, states[1], cu, slots, outs[1], width, 0.7, tiled=True)
+        ops.mingru_scan(proj, bz, bu, states[2], cu, slots, outs[2], width, 0.7, tiled=True, max_new=max(counts), scratch=scratch)
+        p64 = proj.double().cpu()
+        z = torch.sigmoid(p64[:, :width] + bz.double().cpu())
+        u = p64[:, width:2 * width] + bu.double().cpu()
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        gate = torch.nn.functional.silu(p64[:, 2 * width:])
+        ref = torch.zeros(T, width, dtype=torch.float64)
+        for b, n in enumerate(counts):
+            S = ref_state[int(slots[b])]
+            for t in range(int(cu[b]), int(cu[b]) + n):
+                S = (1 - z[t]) * S + z[t] * cand[t]
+                ref[t] = 0.7 * S * gate[t]
+            ref_state[int(slots[b])] = S
+        tol = (2e-5 if dtype == torch.float32 else 0.01) * max(1.0, float(ref.abs().max()))
+        for form, (o, st) in enumerate(zip(outs, states)):
+            assert float((o.double().cpu() - ref).abs().max()) < tol, form
+            assert float((st.double().cpu() - ref_state).abs().max()) < 2e-5 * max(1.0, float(ref_state.abs().max())), form
+
+
+@pytest.mark.parametrize("kind", ["relu_squared", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("rows,n,k", [(5, 256, 128), (70, 264, 192), (200, 512, 256), (1500, 1024, 512), (3, 100, 60)])
+def test_product_with_the_activation_where_it_finishes(kind, rows, n, k):
+    """The serving set's product with its activation in one (the tensor-core product's last step, or the pass that
+    rounds the sums of a product whose K is split) against the float64 statement, for row counts that take each
+    of its ways and for sizes that none of them takes."""
+    from supersonic_b200.csrc.kernel_sets import kernel_set_for
+    g = torch.Generator(device=DEV).manual_seed(rows + n)
+    x = torch.randn(rows, k, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(n, k, device=DEV, generator=g) * k ** -0.5).bfloat16()
+    u = x.double() @ w.double().T
+    ref = {"relu_squared": lambda v: torch.relu(v) ** 2, "silu": torch.nn.functional.silu,
+           "gelu_tanh": lambda v: torch.nn.functional.gelu(v, approximate="tanh")}[kind](u) * 0.3
+    for deterministic in (False, True):
+        ks = kernel_set_for(torch.bfloat16, deterministic=deterministic)
+        for _ in range(2):                                  # the scratch of a split product is left clean for the next
+            out = torch.zeros(rows, n, device=DEV, dtype=torch.bfloat16)
+            ks.linear_activation(x, w, out, kind, 0.3)
+            assert float((out.double() - ref).abs().max()) < 0.01 * max(1.0, float(ref.abs().max())), deterministic
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_dense_feed_forward_norm_and_embedding_alone(dtype):
     from supersonic_b200.parts import EMBEDDINGS, FEED_FORWARDS, NORMS
     from supersonic_b200.engine import StepEntry
