@@ -286,7 +286,7 @@ def test_stream_after_every_layer():
     """float32: the stream after every layer (one that runs with another's tensors counts as a layer of its own),
     and the logits, against the plain statement."""
     from supersonic_b200.engine import StepEntry
-    for name in ("A", "B", "C", "D"):
+    for name in ("A", "B", "C", "D", "E"):
         cfg, store, plain = tr.build(name)
         model = make_model(cfg, store, torch.float32)
         tokens = tokens_of(cfg, 90, 3)
@@ -302,7 +302,7 @@ def test_stream_after_every_layer():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "E"])
 def test_portions_of_every_size_and_token_by_token(dtype, name):
     cfg, store, plain = tr.build(name)
     model = make_model(cfg, store, dtype)
@@ -344,7 +344,7 @@ def test_sizes_that_no_fast_kernel_takes_and_sizes_that_all_take(dtype, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "D"])
+@pytest.mark.parametrize("name", ["A", "D", "E"])
 def test_unequal_batches_against_each_alone_and_reused_slots(dtype, name):
     """Requests of 1 to 260 tokens start together and decode together, the short ones ending first; then other
     requests run in the slots, pages, pooled rows and state rows those gave back."""

@@ -78,7 +78,15 @@ D = model(256, 128, 1e-6, 2.0, 0.5,
            with_mlp(pooled(8, 1, 128, 64, 64, 8, 128, 700.0), 64),
            with_mlp(kept(2, 2, 64, 64, 40, 66, 16, 100.0), 128)])
 
-CONFIGS = {"A": (A, 21, 0.3), "B": (B, 22, 0.35), "C": (C, 23, 0.4), "D": (D, 24, 0.2)}
+# another order: a recurrent layer first; recurrent and kept-token layers that run again with their tensors on state
+# and pages of their own; no kept token at all; runs of one token (every token behind the window stays visible as
+# its own run); a rotation over the whole head and none; head sizes between the tensor-core kernel's tile sizes
+_e = [with_mlp(gru(96), 192),
+      with_mlp(kept(4, 1, 40, 24, 33, 0, 40, 900.0), None),
+      with_mlp(pooled(6, 2, 96, 48, 50, 1, 96, 5000.0, factor=3.0, softcap=50.0), 64)]
+E = model(200, 96, 1e-5, 9.8, 0.25, _e + [again(_e, 0), again(_e, 1), with_mlp(pooled(2, 2, 32, 32, 70, 64, 0, 10.0), 40)])
+
+CONFIGS = {"A": (A, 21, 0.3), "B": (B, 22, 0.35), "C": (C, 23, 0.4), "D": (D, 24, 0.2), "E": (E, 25, 0.3)}
 
 
 def build(name_or_cfg, seed=0, std=0.3):
