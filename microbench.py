@@ -296,6 +296,66 @@ def sigmoid_attention(args):
             "context": ctx, "chunk": c, "us": round(us, 2), "TFLOP/s": round(4.0 * pairs * H * d / us / 1e6, 2)}
 
 
+def window_attention(args):
+    """Softmax attention over a window of --window tokens with --keep kept first tokens or pooled runs of --pool
+    tokens, scores capped at --cap, values turned (--turn): --seqs prompts of --tokens tokens (or, with --tokens 1,
+    decode steps at --context), --heads over --kv-heads heads of --head-dim."""
+    H, G, d, B, T, ps = args.heads, args.kv_heads, args.head_dim, args.seqs, args.tokens, 6
+    W, P, F = args.window, args.pool, args.keep
+    ctx = args.context if T == 1 else T
+    pages = -(-ctx // 64)
+    kc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
+    vc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
+    table = (torch.arange(B * pages, dtype=torch.int32, device=DEV) + 1).view(B, pages).contiguous()
+    pooled = None
+    if P:
+        pp = -(-(ctx // P) // 64) or 1
+        pooled = ((torch.randn(B * pp + 1, G, 64, d, device=DEV) * 0.5).bfloat16(),
+                  (torch.randn(B * pp + 1, G, 64, d, device=DEV) * 0.5).bfloat16(),
+                  (torch.arange(B * pp, dtype=torch.int32, device=DEV) + 1).view(B, pp).contiguous())
+    q = (torch.randn(B * T, H * d, device=DEV) * 0.5).bfloat16()
+    start = ctx - T
+    pos = (torch.arange(T, dtype=torch.int32, device=DEV) + start).repeat(B)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(T)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    seq_start = torch.full((B,), start, dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    vcos = vsin = None
+    if args.turn:
+        angle = torch.arange(ctx, device=DEV).float()[:, None] * (10000.0 ** (-torch.arange(d // 2, device=DEV).float() * 2 / d))
+        vcos, vsin = angle.cos().contiguous(), angle.sin().contiguous()
+    out = torch.empty(B * T, H * d, device=DEV, dtype=torch.bfloat16)
+    cap, sink = (args.cap or None), (True if F else None)
+    if args.kernel == "plain":
+        fn = lambda i: ops.window_attention_plain(q, kc, vc, table, pooled, pos, slot, out, H, G, d, d, ps, W, F, P, d ** -0.5,
+                                                  cap, sink, vcos, vsin, False)
+    else:
+        fn = lambda i: ops.window_attention_mma(q, kc, vc, table, pooled, cu, seq_start, seq_slot, out, T, H, G, d, d, ps, W, F,
+                                                P, d ** -0.5, cap, sink, vcos, vsin, False)
+    us = _time(fn, args.iters)
+    lo = lambda p: max(0, p - W + 1)
+    pairs = sum(p - lo(p) + 1 + (lo(p) // P if P else min(F, lo(p))) for p in range(start, ctx)) * B
+    return {"kernel": "window_attention_" + ("plain" if args.kernel == "plain" else "mma"), "seqs": B, "tokens": T,
+            "context": ctx, "window": W, "pool": P, "keep": F, "us": round(us, 2),
+            "TFLOP/s": round(4.0 * pairs * H * d / us / 1e6, 2)}
+
+
+def mingru_scan(args):
+    """minGRU over --seqs prompts of --tokens tokens and --n channels: --kernel walk, tiled or chunked."""
+    C, T, B = args.n, args.tokens, args.seqs
+    proj = torch.randn(B * T, 3 * C, device=DEV).bfloat16()
+    bz, bu = (torch.randn(C, device=DEV) for _ in range(2))
+    state = torch.zeros(B + 1, C, device=DEV)
+    cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    out = torch.empty(B * T, C, device=DEV, dtype=torch.bfloat16)
+    scratch = torch.empty(ops.mingru_scan_scratch(B, T, C), device=DEV) if args.kernel == "chunked" else None
+    us = _time(lambda i: ops.mingru_scan(proj, bz, bu, state, cu, slots, out, C, 1.0, tiled=args.kernel != "walk", max_new=T,
+                                         scratch=scratch), args.iters)
+    return {"kernel": "mingru_scan_" + args.kernel, "seqs": B, "tokens": T, "channels": C, "us": round(us, 2),
+            "GB/s": round(B * T * C * 8 / us / 1e3, 1)}
+
+
 def sampling(args):
     """The pick of a step: argmax at temperature 0, else a draw under the given cuts.  Eight sets of
     logits in turn (64 rows of 128,256 are 33 MB each)."""
@@ -318,7 +378,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
     for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling", "latent_attention", "grouped_gemm",
-                 "gated_linear_scan", "matrix_state_scan", "gated_unit_scan", "sigmoid_attention"):
+                 "gated_linear_scan", "matrix_state_scan", "gated_unit_scan", "sigmoid_attention", "window_attention",
+                 "mingru_scan"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--heads", type=int, default=32)
@@ -351,6 +412,11 @@ def main(argv=None):
         p.add_argument("--experts", type=int, default=64)
         p.add_argument("--top", type=int, default=6)
         p.add_argument("--chunk", type=int, default=128, help="gated_linear_scan: tokens a chunk (0: in one go); sigmoid_attention: positions a chunk")
+        p.add_argument("--window", type=int, default=512, help="window_attention: tokens a query sees behind it")
+        p.add_argument("--pool", type=int, default=0, help="window_attention: tokens a pooled run (0: none)")
+        p.add_argument("--keep", type=int, default=0, help="window_attention: kept first tokens (with a sink)")
+        p.add_argument("--cap", type=float, default=0.0, help="window_attention: score cap (0: none)")
+        p.add_argument("--turn", action="store_true", help="window_attention: values stored turned by their position")
     args = ap.parse_args(argv)
     print(json.dumps(globals()[args.what](args)))
 

@@ -11,8 +11,9 @@
 // S_out = A S_in + B, the pairs are folded in order through shared memory, and each warp then walks its tokens
 // again from its true entry state; both forms compute a_t S + b_t with a_t = 1 - z_t, b_t = z_t cand_t.
 // The chunked scan for prompts: the same tile, but every tile of 64 tokens has a block of its own.  A first launch
-// composes each tile into one pair (A, B) and keeps the entering state aside; a second launch folds the pairs of
-// the tiles before its own from that state, walks its tokens, and the last tile's block writes the state back.
+// composes each tile into one pair (A, B); a small second one folds the pairs in order from the sequence's state,
+// leaves every tile's entering state in the pair's place and writes the final state back; a third walks each
+// tile's tokens from its entering state.
 #include "common.cuh"
 #include <math.h>
 
@@ -150,8 +151,9 @@ mingru_scan_tiled_kernel(const P* __restrict__ proj, int ld, const float* __rest
     }
 }
 
-// Chunked scan.  scratch: per sequence max_chunks pairs [A | B] of `width` floats each, then the entering state.
-// PHASE 0 composes, PHASE 1 folds, walks and writes.  FAST: sigmoids from the fast exponential (bfloat16 rows).
+// Chunked scan.  scratch: per sequence max_chunks pairs [A | B] of `width` floats each (and one spare row).
+// PHASE 0 composes; mingru_fold_kernel folds the pairs in order; PHASE 1 walks each tile from its entering state.
+// FAST: sigmoids from the fast exponential (bfloat16 rows).
 template <bool FAST> __device__ __forceinline__ float mg_sig(float x) {
     return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
 }
@@ -185,7 +187,6 @@ mingru_scan_chunked_kernel(const P* __restrict__ proj, int ld, const float* __re
     const int n_chunks = (n_new + MG_WARPS * L - 1) / (MG_WARPS * L);
     if (chunk >= n_chunks) return;
     float* pairs = scratch + (size_t)b * (2 * max_chunks + 1) * width;
-    float* entering = pairs + (size_t)2 * max_chunks * width;
     const int first = chunk * MG_WARPS * L + warp * L;
     float a[L][2], bb[L][2];
     float A[2] = {1.f, 1.f}, B[2] = {0.f, 0.f};
@@ -224,23 +225,15 @@ mingru_scan_chunked_kernel(const P* __restrict__ proj, int ld, const float* __re
                 }
             *reinterpret_cast<float2*>(pairs + (size_t)(2 * chunk) * width + c) = make_float2(Ac[0], Ac[1]);
             *reinterpret_cast<float2*>(pairs + (size_t)(2 * chunk + 1) * width + c) = make_float2(Bc[0], Bc[1]);
-            if (chunk == 0)
-                *reinterpret_cast<float2*>(entering + c) = *reinterpret_cast<const float2*>(state + (size_t)slot * width + c);
         }
         return;
     }
     if (!live) return;
-    // the state that enters this tile: the sequence's, through the pairs of the tiles before
+    // the state that enters this tile: the fold over the tiles before it left it where the tile's A was
     float S[2];
     {
-        const float2 s0 = *reinterpret_cast<const float2*>(entering + c);
+        const float2 s0 = *reinterpret_cast<const float2*>(pairs + (size_t)(2 * chunk) * width + c);
         S[0] = s0.x; S[1] = s0.y;
-    }
-    for (int ch = 0; ch < chunk; ++ch) {
-        const float2 Ap = *reinterpret_cast<const float2*>(pairs + (size_t)(2 * ch) * width + c);
-        const float2 Bp = *reinterpret_cast<const float2*>(pairs + (size_t)(2 * ch + 1) * width + c);
-        S[0] = fmaf(Ap.x, S[0], Bp.x);
-        S[1] = fmaf(Ap.y, S[1], Bp.y);
     }
     float s[2] = {S[0], S[1]};                             // the state that enters this warp's tokens
 #pragma unroll
@@ -262,10 +255,27 @@ mingru_scan_chunked_kernel(const P* __restrict__ proj, int ld, const float* __re
         MgPair<T>::store(out + (size_t)(t0 + first + i) * ldo + c, s[0] * (g0 * mg_sig<FAST>(g0)) * out_scale,
                          s[1] * (g1 * mg_sig<FAST>(g1)) * out_scale);
     }
-    if (chunk == n_chunks - 1 && warp == 0) {
-        state[(size_t)slot * width + c] = S[0];
-        state[(size_t)slot * width + c + 1] = S[1];
+}
+
+// Between the two: a thread per sequence and channel folds the tiles' pairs in order from the sequence's state,
+// leaves each tile's entering state where its A was, and writes the state behind the last tile back.
+__global__ void __launch_bounds__(128)
+mingru_fold_kernel(float* __restrict__ state, const int* __restrict__ cu_new, const int* __restrict__ seq_slot, int width,
+                   float* __restrict__ scratch, int max_chunks, int chunk_tokens) {
+    const int c = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
+    const int slot = seq_slot[b];
+    if (slot < 0 || c >= width) return;
+    const int n_new = cu_new[b + 1] - cu_new[b];
+    const int n_chunks = (n_new + chunk_tokens - 1) / chunk_tokens;
+    if (n_chunks <= 0) return;
+    float* pairs = scratch + (size_t)b * (2 * max_chunks + 1) * width;
+    float S = state[(size_t)slot * width + c];
+    for (int ch = 0; ch < n_chunks; ++ch) {
+        const float A = pairs[(size_t)(2 * ch) * width + c], B = pairs[(size_t)(2 * ch + 1) * width + c];
+        pairs[(size_t)(2 * ch) * width + c] = S;
+        S = fmaf(A, S, B);
     }
+    state[(size_t)slot * width + c] = S;
 }
 
 // proj [T, ld] rows [zp | up | gp] of `width` columns each; out [T, ldo]; state [slots, width] float32.
@@ -286,6 +296,9 @@ SSB_API int ssb_mingru_scan(const void* proj, int ld, int proj_dtype, const floa
     {                                                                                                                       \
         rc = ssb_launch(mingru_scan_chunked_kernel<P, T, 8, 0, FAST>, grid, block, 0, stream, pdl != 0, (const P*)proj, ld,  \
                         z_bias, x_bias, state, cu_new, seq_slot, (T*)out, ldo, width, out_scale, scratch, chunks);          \
+        if (!rc)                                                                                                            \
+            rc = ssb_launch(mingru_fold_kernel, dim3((width + 127) / 128, n_seqs), dim3(128), 0, stream, false, state,       \
+                            cu_new, seq_slot, width, scratch, chunks, MG_WARPS * 8);                                        \
         if (!rc)                                                                                                            \
             rc = ssb_launch(mingru_scan_chunked_kernel<P, T, 8, 1, FAST>, grid, block, 0, stream, false, (const P*)proj, ld, \
                             z_bias, x_bias, state, cu_new, seq_slot, (T*)out, ldo, width, out_scale, scratch, chunks);      \
