@@ -62,8 +62,8 @@ class PlainKernels:
     def _chain(self, rows) -> bool:
         return bool(self.pdl) and int(rows) <= self.PDL_MAX_ROWS
 
-    def embed(self, ids, table, out):
-        ops.embed(ids, table, out)
+    def embed(self, ids, table, out, scale=1.0):
+        ops.embed(ids, table, out, scale)
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
         ops.rmsnorm(x, weight, eps, out, rows)
@@ -235,10 +235,12 @@ class PlainKernels:
         self.activation(u, out, kind, scale)
 
     def qkv_prepare(self, qkv, q_weight, k_weight, norm, eps, position, value_position, kv, batch, n_q, n_kv, dim, vdim,
-                    page_shift, write_cache=True):
+                    page_shift, write_cache=True, pooled_kv=None, pool=0) -> bool:
         """Norm of q and k (``norm`` ``"head"``, ``"row"`` or None), rotation of their first coordinates by
         ``position``, of the values over their whole width by ``value_position`` (either may be None), k and v into
-        the cache."""
+        the cache.  With a pooled store and a step of one token a sequence, the tokens that end a run of ``pool``
+        tokens write the run's pooled row too; True says so (else the caller runs ``pool_rows``)."""
+        pools = bool(pool) and pooled_kv is not None and write_cache and batch.is_decode
         cos = sin = vcos = vsin = None
         rot_dims, inter, v_inter = 0, False, False
         if position is not None:
@@ -252,7 +254,8 @@ class PlainKernels:
         k_cache, v_cache, table, _ = kv
         ops.qkv_prepare(qkv, q_weight, k_weight, norm, eps, cos, sin, rot_dims, inter, vcos, vsin, v_inter, batch.pos,
                         batch.slot_of_token, table, k_cache, v_cache, n_q, n_kv, dim, vdim, page_shift, write_cache,
-                        pdl=self._chain(batch.n_tokens))
+                        pdl=self._chain(batch.n_tokens), pooled=pooled_kv[:3] if pools else None, pool=pool if pools else 0)
+        return pools
 
     def pool_rows(self, kv, pooled_kv, batch, n_kv, dim, vdim, page_shift, pool):
         """The mean key and value row of every run of ``pool`` tokens that the step's tokens finish."""

@@ -83,16 +83,16 @@ def _fn(lib: str, name: str):
 
 
 # ---- plain ops -------------------------------------------------------------------------
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] into the float32 residual stream."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale into the float32 residual stream (the product is float32)."""
     _need(ids, "ids", torch.int32, 1); _need(table, "table", None, 2); _need(out, "out", torch.float32, 2)
     if not (table.is_contiguous() and out.is_contiguous()):
         raise KernelError("embed: table and out must be contiguous")
     if out.shape[0] != ids.shape[0] or out.shape[1] != table.shape[1]:
         raise KernelError(f"embed: out {tuple(out.shape)} does not fit {ids.shape[0]} ids of width {table.shape[1]}")
-    _check(_fn("plain_ops", "ssb_embed")(
+    _check(_fn("plain_ops", "ssb_embed_scaled")(
         _ptr(ids), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(out), c_int(ids.shape[0]),
-        c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed")
+        c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -904,13 +904,16 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
                 eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dims: int, interleaved: bool,
                 v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_interleaved: bool, pos: torch.Tensor,
                 slot: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int,
-                n_kv: int, dim: int, vdim: int, page_shift: int, write_cache: bool = True, pdl: bool = False) -> None:
+                n_kv: int, dim: int, vdim: int, page_shift: int, write_cache: bool = True, pdl: bool = False,
+                pooled=None, pool: int = 0) -> None:
     """Rows [q (n_q x dim) | k (n_kv x dim) | v (n_kv x vdim)].  ``norm`` ``"head"``: every q and k head is divided
     by its root mean square (eps inside the root) and multiplied by a weight vector [dim] shared by the heads;
     ``"row"``: all heads of q (of k) together are divided by one root mean square, weights [heads x dim]; None:
     no norm.  Then the first ``rot_dims`` coordinates of every q and k head are turned by the token's position, and
     with ``v_cos``/``v_sin`` [positions, vdim / 2] every value head over its whole width.  q is written back in
-    place; k and v go to the token's place in the paged cache."""
+    place; k and v go to the token's place in the paged cache.  ``pooled`` = (keys, values, page table) of a store
+    with a row per run of ``pool`` tokens, only for steps that bring one token a sequence: the token that ends a
+    run writes the run's pooled row as ``pool_rows`` would."""
     _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     if norm not in QK_NORM_MODES:
@@ -939,12 +942,22 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
         _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype)
         if not (k_cache.is_contiguous() and v_cache.is_contiguous()) or k_cache.shape[-1] != dim or v_cache.shape[-1] != vdim:
             raise KernelError("qkv_prepare: cache rows of dim and vdim, contiguous")
+    pk = pv = ptable = None
+    if pool:
+        if not write_cache or pooled is None:
+            raise KernelError("qkv_prepare: pooling needs the cache written and the pooled store")
+        pk, pv, ptable = pooled[:3]
+        _need(pk, "pooled keys", qkv.dtype); _need(pv, "pooled values", qkv.dtype); _need(ptable, "pooled page table", torch.int32, 2)
+        if pk.shape[-1] != dim or pv.shape[-1] != vdim or not (pk.is_contiguous() and pv.is_contiguous()):
+            raise KernelError("qkv_prepare: pooled rows of dim and vdim, contiguous")
     _check(_fn("window_attention", "ssb_qkv_prepare")(
         _ptr(qkv), c_int(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), _ptr(q_weight), _ptr(k_weight), c_int(mode),
         c_float(eps), _ptr(cos), _ptr(sin), c_int(rot_dims), c_int(1 if interleaved else 0), _ptr(v_cos), _ptr(v_sin),
         c_int(1 if v_interleaved else 0), c_int(positions), _ptr(pos), _ptr(slot), _ptr(page_table),
         c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim),
-        c_int(page_shift), c_int(1 if write_cache else 0), c_int(1 if pdl else 0), _stream()), "qkv_prepare")
+        c_int(page_shift), c_int(1 if write_cache else 0), _ptr(pk), _ptr(pv), _ptr(ptable),
+        c_int(ptable.shape[1] if ptable is not None else 0), c_int(int(pool) if pool else 0), c_int(1 if pdl else 0),
+        _stream()), "qkv_prepare")
 
 
 def pool_rows(k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, pk_cache: torch.Tensor,

@@ -19,11 +19,11 @@
 typedef __nv_bfloat16 bf16;
 
 // ---------------------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :], written into the float32 residual stream
+// embedding: out[t, :] = table[ids[t], :] * scale, written into the float32 residual stream
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = out + (size_t)t * hidden;
@@ -32,19 +32,27 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
         return;
     }
     const T* src = table + (size_t)id * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ssb_to_float(src[c]);
+    if (scale == 1.0f)
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ssb_to_float(src[c]);
+    else
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ssb_to_float(src[c]) * scale;
+}
+
+SSB_API int ssb_embed_scaled(const int* ids, const void* table, int table_dtype, float* out, int n_tokens,
+                             int hidden, int vocab, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (table_dtype == SSB_F32)
+        embed_kernel<float><<<n_tokens, 256, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, scale);
+    else if (table_dtype == SSB_BF16)
+        embed_kernel<bf16><<<n_tokens, 256, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, scale);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return ssb_launch_status();
 }
 
 SSB_API int ssb_embed(const int* ids, const void* table, int table_dtype, float* out, int n_tokens,
                       int hidden, int vocab, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (table_dtype == SSB_F32)
-        embed_kernel<float><<<n_tokens, 256, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
-    else if (table_dtype == SSB_BF16)
-        embed_kernel<bf16><<<n_tokens, 256, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
-    else
-        return SSB_ERR_BAD_DTYPE;
-    return ssb_launch_status();
+    return ssb_embed_scaled(ids, table, table_dtype, out, n_tokens, hidden, vocab, 1.0f, stream);
 }
 
 // ---------------------------------------------------------------------------------------

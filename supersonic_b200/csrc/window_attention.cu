@@ -72,7 +72,8 @@ __device__ __forceinline__ void wa_pair(int c, int dims, int interleaved, int& o
 //             2: the whole row (all heads) divided by one root mean square, weights [heads * dim].
 //   q and k: the first rot_dims coordinates of every head turned by the token's position (tables [positions,
 //   rot_dims / 2]); v: all vdim coordinates turned (tables [positions, vdim / 2]) if v tables are given.
-// q is written back in place, k and v go to the token's row of the paged cache.
+// q is written back in place, k and v go to the token's row of the paged cache.  In a step that brings one token a
+// sequence, the token that ends a run of `pool` tokens may write the run's pooled row as well (see pool_rows).
 // ---------------------------------------------------------------------------------------
 constexpr int WP_THREADS = 256;
 
@@ -83,7 +84,8 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
                    int interleaved, const float* __restrict__ vcos_t, const float* __restrict__ vsin_t, int v_interleaved,
                    int table_positions, const int* __restrict__ pos, const int* __restrict__ slot,
                    const int* __restrict__ page_table, int max_pages, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                   int n_q, int n_kv, int dim, int vdim, int page_shift, int write_cache) {
+                   int n_q, int n_kv, int dim, int vdim, int page_shift, int write_cache, T* __restrict__ pk_cache,
+                   T* __restrict__ pv_cache, const int* __restrict__ pool_table, int pool_max_pages, int pool) {
     extern __shared__ float wp_row[];                      // the part's row, then one factor per head
     __shared__ float red[WP_THREADS / 32];
     ssb_pdl_launch_dependents();
@@ -94,6 +96,22 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
     if (part > 0 && !write_cache) return;
     const int p = pos[t];
     T* base = qkv + (size_t)t * ld;
+    // pool > 0 (steps of one token a sequence only): the token that ends a run of `pool` tokens also writes the
+    // run's pooled row, the mean of the cached rows in rising order (the other rows came with earlier steps, this
+    // token's own was written by this block: the barrier orders it before the reads)
+    auto pool_run = [&](const T* cache, T* pooled, int width) {
+        if (pool <= 0 || (p + 1) % pool) return;
+        __syncthreads();
+        const int run = p / pool;
+        const float inv_pool = 1.0f / (float)pool;
+        for (int c = tid; c < n_kv * width; c += WP_THREADS) {
+            const int h = c / width, d = c - h * width;
+            float sum = 0.f;
+            for (int j = 0; j < pool; ++j)
+                sum += ssb_to_float(cache[ssb_cache_row(page_table, max_pages, s, run * pool + j, page_shift, n_kv, h, width) + d]);
+            pooled[ssb_cache_row(pool_table, pool_max_pages, s, run, page_shift, n_kv, h, width) + d] = ssb_from_float<T>(sum * inv_pool);
+        }
+    };
     if (part == 2) {
         const T* src = base + (size_t)(n_q + n_kv) * dim;
         const int n = n_kv * vdim;
@@ -112,6 +130,7 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
             }
             v_cache[ssb_cache_row(page_table, max_pages, s, p, page_shift, n_kv, h, vdim) + d] = ssb_from_float<T>(v);
         }
+        pool_run(v_cache, pv_cache, vdim);
         return;
     }
     const int heads = part == 0 ? n_q : n_kv;
@@ -161,16 +180,19 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
         if (part == 0) src[c] = ssb_from_float<T>(v);
         else k_cache[ssb_cache_row(page_table, max_pages, s, p, page_shift, n_kv, h, dim) + d] = ssb_from_float<T>(v);
     }
+    if (part == 1) pool_run(k_cache, pk_cache, dim);
 }
 
 SSB_API int ssb_qkv_prepare(void* qkv, int ld, int dtype, const float* q_w, const float* k_w, int norm_mode, float eps,
                             const float* cos_t, const float* sin_t, int rot_dims, int interleaved, const float* vcos_t,
                             const float* vsin_t, int v_interleaved, int table_positions, const int* pos, const int* slot,
                             const int* page_table, int max_pages, void* k_cache, void* v_cache, int n_tokens, int n_q,
-                            int n_kv, int dim, int vdim, int page_shift, int write_cache, int pdl, cudaStream_t stream) {
+                            int n_kv, int dim, int vdim, int page_shift, int write_cache, void* pk_cache, void* pv_cache,
+                            const int* pool_table, int pool_max_pages, int pool, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dim <= 0 || vdim <= 0 || n_q <= 0 || n_kv <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) ||
-        norm_mode < 0 || norm_mode > 2 || (vcos_t != nullptr && (vdim & 1)))
+        norm_mode < 0 || norm_mode > 2 || (vcos_t != nullptr && (vdim & 1)) || pool < 0 ||
+        (pool > 0 && (!write_cache || !pk_cache || !pv_cache || !pool_table)))
         return SSB_ERR_BAD_SIZE;
     const int widest = max(n_q * dim, max(n_kv * dim, n_kv * vdim));
     const size_t smem = ((size_t)widest + (size_t)max(n_q, n_kv)) * sizeof(float);
@@ -187,7 +209,7 @@ SSB_API int ssb_qkv_prepare(void* qkv, int ld, int dtype, const float* q_w, cons
         rc = ssb_launch(kern, grid, dim3(WP_THREADS), smem, stream, pdl != 0, (TYPE*)qkv, ld, q_w, k_w, norm_mode, eps,   \
                         cos_t, sin_t, rot_dims, interleaved, vcos_t, vsin_t, v_interleaved, table_positions, pos, slot,   \
                         page_table, max_pages, (TYPE*)k_cache, (TYPE*)v_cache, n_q, n_kv, dim, vdim, page_shift,          \
-                        write_cache);                                                                                     \
+                        write_cache, (TYPE*)pk_cache, (TYPE*)pv_cache, pool_table, pool_max_pages, pool);                 \
     }
     if (dtype == SSB_F32) SSB_WP(float)
     else if (dtype == SSB_BF16) SSB_WP(bf16)

@@ -24,9 +24,7 @@ class Embedding:
 
     def __call__(self, ctx, token_ids):
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
-        ctx.kernels.embed(token_ids, self.table, out)
-        if self.scale != 1.0:
-            ctx.kernels.scale_(out, self.scale)
+        ctx.kernels.embed(token_ids, self.table, out, self.scale)
         return out
 
 

@@ -113,9 +113,10 @@ class WindowAttention:
         width = self.n_q * self.dim + (self.n_kv * (self.dim + self.vdim) if writes_cache else 0)
         qkv = torch.empty((T, width), dtype=self.dtype, device=dev)
         k.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
-        k.qkv_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm, self.eps, position, self.value_position, kv,
-                      ctx.batch, self.n_q, self.n_kv, self.dim, self.vdim, PAGE_SHIFT, writes_cache)
-        if self.pool and writes_cache:
+        pooled_there = k.qkv_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm, self.eps, position, self.value_position, kv,
+                                     ctx.batch, self.n_q, self.n_kv, self.dim, self.vdim, PAGE_SHIFT, writes_cache,
+                                     pooled_kv=pooled if writes_cache else None, pool=self.pool)
+        if self.pool and writes_cache and not pooled_there:
             k.pool_rows(kv, pooled, ctx.batch, self.n_kv, self.dim, self.vdim, PAGE_SHIFT, self.pool)
         heads = torch.empty((T, self.n_q * self.vdim), dtype=self.dtype, device=dev)
         k.window_attention(qkv, kv, pooled, ctx.batch, heads, self.n_q, self.n_kv, self.dim, self.vdim, PAGE_SHIFT,
