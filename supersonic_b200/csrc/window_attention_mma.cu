@@ -3,7 +3,7 @@
 //
 // A block takes one sequence, one kv head and a tile of query rows; a row is a (new token, query head of the kv
 // head's group) pair, heads fastest, so that the heads that share a kv head share its pages.  What the rows can
-// see is streamed once, 64 keys at a time, through a two-stage cp.async ring, from three sources in a fixed
+// see is streamed once, 64 keys at a time, through a cp.async ring (two stages, four in decode steps), from three sources in a fixed
 // order: the pages of the pooled store (64 runs a page), the pages that hold the kept first tokens, and the
 // pages from the first row's window start to the last row's position.  Per 64 keys a warp takes S = Q K^T for
 // its rows, scales and caps the scores, masks what a row does not see, keeps a running maximum and sum per row
@@ -23,6 +23,9 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int WM_THREADS = 128;
 constexpr int WM_PAGE = 64;
+// Blocks that fill the SMs hide one another's waits: two pages in the ring, and more blocks an SM.  A decode step of a
+// few sequences has fewer blocks than SMs, each waiting for its next page: three pages in flight beside the one at work.
+constexpr int WM_DEEP_MAX_BLOCKS = 148;
 
 // tanh from one exponential: 1 - 2 / (1 + e^(2y)); absolute error of a few float32 ulps of 1
 __device__ __forceinline__ float wm_tanh(float y) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * y)); }
@@ -40,15 +43,15 @@ struct WmArgs {
     float out_scale;
 };
 
-template <int DIM, int VDIM, bool SPLIT>
+template <int DIM, int VDIM, bool SPLIT, int ST>          // ST: pages in the ring
 __global__ void __launch_bounds__(WM_THREADS)
 window_attention_mma_kernel(const WmArgs a) {
     constexpr int ROWS = SPLIT ? 16 : 64;
     constexpr int KP = DIM + 8, VP = VDIM + 8;            // padded rows: ldmatrix without bank conflicts
     constexpr int NT = SPLIT ? 2 : 8;                     // key tiles of 8 a warp takes of a page
     extern __shared__ __align__(16) unsigned char wm_smem[];
-    bf16* Ks = reinterpret_cast<bf16*>(wm_smem);          // [2][64][KP]
-    bf16* Vs = Ks + 2 * WM_PAGE * KP;                     // [2][64][VP]
+    bf16* Ks = reinterpret_cast<bf16*>(wm_smem);          // [ST][64][KP]
+    bf16* Vs = Ks + ST * WM_PAGE * KP;                    // [ST][64][VP]
     __shared__ float m_s[4][16], l_s[4][16], f_s[4][16];
     const int b = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
@@ -75,31 +78,44 @@ window_attention_mma_kernel(const WmArgs a) {
 
     // the padding columns stay zero: no copy writes them
     if (dim < DIM || vdim < VDIM) {
-        for (int c = tid; c < 2 * WM_PAGE * (DIM - dim); c += WM_THREADS)
+        for (int c = tid; c < ST * WM_PAGE * (DIM - dim); c += WM_THREADS)
             Ks[(c / (DIM - dim)) * KP + dim + c % (DIM - dim)] = __float2bfloat16_rn(0.f);
-        for (int c = tid; c < 2 * WM_PAGE * (VDIM - vdim); c += WM_THREADS)
+        for (int c = tid; c < ST * WM_PAGE * (VDIM - vdim); c += WM_THREADS)
             Vs[(c / (VDIM - vdim)) * VP + vdim + c % (VDIM - vdim)] = __float2bfloat16_rn(0.f);
     }
 
-    auto load_tile = [&](int t, int stage) {
+    // the page of tile t; read a turn before the tile's copies are issued, so that they do not wait for it
+    auto tile_page = [&](int t) -> int {
+        if (t >= n_tiles) return 0;
+        return t < t_pool ? pool_pages[t] : pages[t < t_pool + t_keep ? t - t_pool : page_lo + (t - t_pool - t_keep)];
+    };
+    auto load_tile = [&](int t, int stage, int id) {
         const bool pooled = t < t_pool;
-        const int id = pooled ? pool_pages[t] : pages[t < t_pool + t_keep ? t - t_pool : page_lo + (t - t_pool - t_keep)];
         const bf16* ksrc = (pooled ? a.pk_cache : a.k_cache) + ((size_t)id * n_kv + kvh) * WM_PAGE * dim;
         const bf16* vsrc = (pooled ? a.pv_cache : a.v_cache) + ((size_t)id * n_kv + kvh) * WM_PAGE * vdim;
         bf16* kd = Ks + stage * WM_PAGE * KP;
         bf16* vd = Vs + stage * WM_PAGE * VP;
+        // 16-byte pieces counted over the padded row (a power of two: shifts, no division); those past the real row are skipped
         const int kc = dim >> 3, vc = vdim >> 3;
-        for (int c = tid; c < WM_PAGE * kc; c += WM_THREADS) {
-            const int r = c / kc, cc = c - r * kc;
-            cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * KP + cc * 8), ksrc + r * dim + cc * 8);
+#pragma unroll
+        for (int c = tid; c < WM_PAGE * (DIM / 8); c += WM_THREADS) {
+            const int r = c / (DIM / 8), cc = c % (DIM / 8);
+            if (cc < kc) cp_async16((uint32_t)__cvta_generic_to_shared(kd + r * KP + cc * 8), ksrc + r * dim + cc * 8);
         }
-        for (int c = tid; c < WM_PAGE * vc; c += WM_THREADS) {
-            const int r = c / vc, cc = c - r * vc;
-            cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * VP + cc * 8), vsrc + r * vdim + cc * 8);
+#pragma unroll
+        for (int c = tid; c < WM_PAGE * (VDIM / 8); c += WM_THREADS) {
+            const int r = c / (VDIM / 8), cc = c % (VDIM / 8);
+            if (cc < vc) cp_async16((uint32_t)__cvta_generic_to_shared(vd + r * VP + cc * 8), vsrc + r * vdim + cc * 8);
         }
         cp_async_commit();
     };
-    load_tile(0, 0);
+    // every turn commits one group, an empty one where no page is left: the wait below counts groups
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+        if (i < n_tiles) load_tile(i, i, tile_page(i));
+        else cp_async_commit();
+    }
+    int page_ahead = tile_page(ST - 1);
 
     // this warp's rows: g and g + 8 of its 16
     const int wrow0 = row0 + (SPLIT ? 0 : warp * 16);
@@ -137,13 +153,12 @@ window_attention_mma_kernel(const WmArgs a) {
     const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
 
     for (int t = 0; t < n_tiles; ++t) {
-        const int stage = t & 1;
-        if (t + 1 < n_tiles) {
-            load_tile(t + 1, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int stage = t % ST;
+        const int page_now = page_ahead;
+        page_ahead = tile_page(t + ST);
+        if (t + ST - 1 < n_tiles) load_tile(t + ST - 1, (t + ST - 1) % ST, page_now);   // the stage the turn before this one left
+        else cp_async_commit();
+        cp_async_wait<ST - 1>();
         __syncthreads();
         // index of the tile's first key in its source, and what each row sees of the source: [v_lo, v_hi]
         int kbase, v_lo[2], v_hi[2];
@@ -352,13 +367,13 @@ window_attention_mma_kernel(const WmArgs a) {
     }
 }
 
-template <int DIM, int VDIM, bool SPLIT>
+template <int DIM, int VDIM, bool SPLIT, int ST>
 static int launch_window_mma(const WmArgs& a, int n_seqs, int max_new, int pdl, cudaStream_t stream) {
     constexpr int ROWS = SPLIT ? 16 : 64;
-    const size_t smem = (size_t)2 * WM_PAGE * (DIM + 8 + VDIM + 8) * sizeof(bf16);
+    const size_t smem = (size_t)ST * WM_PAGE * (DIM + 8 + VDIM + 8) * sizeof(bf16);
     static_assert((size_t)2 * WM_PAGE * (DIM + 8 + VDIM + 8) * sizeof(bf16) >= (size_t)64 * VDIM * sizeof(float),
                   "the staged pages make room for the rows' sums");
-    auto kern = window_attention_mma_kernel<DIM, VDIM, SPLIT>;
+    auto kern = window_attention_mma_kernel<DIM, VDIM, SPLIT, ST>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -400,10 +415,13 @@ SSB_API int ssb_window_attention_mma(const void* q, int ldq, const void* k_cache
     a.vcos = vcos_t; a.vsin = vsin_t; a.v_interleaved = v_interleaved; a.table_positions = table_positions;
     a.out_scale = out_scale;
     const int D = dim <= 64 ? 64 : 128, V = vdim <= 64 ? 64 : 128;
+    const long long blocks = (long long)((max_new * (n_q / n_kv) + 15) / 16) * n_kv * n_seqs;     // of the decode form
+    const bool deep = split && blocks <= WM_DEEP_MAX_BLOCKS;
 #define SSB_WM(D_, V_) \
     if (D == D_ && V == V_) \
-        return split ? launch_window_mma<D_, V_, true>(a, n_seqs, max_new, pdl, stream) \
-                     : launch_window_mma<D_, V_, false>(a, n_seqs, max_new, pdl, stream)
+        return !split ? launch_window_mma<D_, V_, false, 2>(a, n_seqs, max_new, pdl, stream) \
+               : deep ? launch_window_mma<D_, V_, true, 4>(a, n_seqs, max_new, pdl, stream) \
+                      : launch_window_mma<D_, V_, true, 2>(a, n_seqs, max_new, pdl, stream)
     SSB_WM(64, 64); SSB_WM(64, 128); SSB_WM(128, 64); SSB_WM(128, 128);
 #undef SSB_WM
     return SSB_ERR_UNSUPPORTED;
