@@ -168,6 +168,33 @@ def test_window_attention_kernels_agree(dim, vdim, heads, kv_heads, window, keep
             assert err < 0.01 * max(1.0, float(want.float().abs().max())), (counts, split, err)
 
 
+def test_window_attention_decode_step_of_many_sequences():
+    """A decode step with more blocks than the device has SMs takes the shallow ring of the decode form: 90
+    sequences of unequal lengths (their page tables point into the same few pages, which are only read) against
+    the plain kernel."""
+    from supersonic_b200.csrc import ops
+    g = torch.Generator(device=DEV).manual_seed(11)
+    heads, kv_heads, dim, vdim, B, pages_per = 8, 2, 64, 64, 90, 5
+    kc = (torch.randn(12, kv_heads, 64, dim, device=DEV, generator=g) * 0.6).bfloat16()
+    vc = (torch.randn(12, kv_heads, 64, vdim, device=DEV, generator=g) * 0.6).bfloat16()
+    pk = (torch.randn(7, kv_heads, 64, dim, device=DEV, generator=g) * 0.6).bfloat16()
+    pv = (torch.randn(7, kv_heads, 64, vdim, device=DEV, generator=g) * 0.6).bfloat16()
+    table = torch.randint(0, 12, (B, pages_per), device=DEV, generator=g).int()
+    pooled = (pk, pv, torch.randint(0, 7, (B, 1), device=DEV, generator=g).int())
+    lens = torch.randint(1, 64 * pages_per, (B,), generator=torch.Generator().manual_seed(3))
+    q = (torch.randn(B, heads * dim, device=DEV, generator=g) * 0.6).bfloat16()
+    pos = (lens - 1).int().to(DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    want, got = (torch.zeros(B, heads * vdim, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+    ops.window_attention_plain(q, kc, vc, table, pooled, pos, slot, want, heads, kv_heads, dim, vdim, 6, 100, 0, 8, dim ** -0.5,
+                               25.0, None, None, None, False)
+    ops.window_attention_mma(q, kc, vc, table, pooled, cu, pos, slot, got, 1, heads, kv_heads, dim, vdim, 6, 100, 0, 8,
+                             dim ** -0.5, 25.0, None, None, None, False)
+    err = float((got.float() - want.float()).abs().max())
+    assert err < 0.01 * max(1.0, float(want.float().abs().max())), err
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,layer", [("A", 2), ("B", 0), ("C", 1), ("D", 1), ("D", 4)])
 def test_window_attention_with_kept_tokens_and_sink_alone(dtype, name, layer):
