@@ -3,6 +3,7 @@ from .base import (BlockSpec, ConfigError, ModelSpec, PartSpec, ScheduleEntry,
                    default_schedule)
 from .llama import LlamaConfig, RopeScaling
 from .ronelorn import RonelornConfig
+from .kilisun import KilisunConfig
 from .sotavik import SotavikConfig
 from .vufadra import VufadraConfig
 from .registry import (config_from_dict, known_architectures, load_config,
@@ -10,6 +11,6 @@ from .registry import (config_from_dict, known_architectures, load_config,
                        register_architecture, spec_from_config)
 
 __all__ = ["BlockSpec", "ConfigError", "ModelSpec", "PartSpec", "ScheduleEntry",
-           "default_schedule", "LlamaConfig", "RopeScaling", "SotavikConfig", "VufadraConfig", "RonelornConfig", "config_from_dict",
+           "default_schedule", "LlamaConfig", "RopeScaling", "SotavikConfig", "VufadraConfig", "RonelornConfig", "KilisunConfig", "config_from_dict",
            "known_architectures", "load_config", "lookup_architecture", "preset_config",
            "preset_names", "register_architecture", "spec_from_config"]

@@ -18,6 +18,7 @@ from .llama import ARCHITECTURE as _LLAMA, LlamaConfig
 from .sotavik import ARCHITECTURE as _SOTAVIK, SotavikConfig
 from .ronelorn import ARCHITECTURE as _RONELORN, RonelornConfig
 from .vufadra import ARCHITECTURE as _VUFADRA, VufadraConfig
+from .kilisun import ARCHITECTURE as _KILISUN, KilisunConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -70,6 +71,7 @@ register_architecture(_LLAMA, LlamaConfig)
 register_architecture(_SOTAVIK, SotavikConfig)
 register_architecture(_VUFADRA, VufadraConfig)
 register_architecture(_RONELORN, RonelornConfig)
+register_architecture(_KILISUN, KilisunConfig)
 
 
 _PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets")

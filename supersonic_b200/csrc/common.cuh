@@ -42,6 +42,17 @@ __device__ __forceinline__ float ssb_activate(float u, int kind) {
     return u / (1.0f + expf(-u));
 }
 
+// A gated unit's inner step between its two products, in float32: what becomes of a gate value g and an up value u.
+//   kind 0: silu(g) * u;
+//   kind 1: with g' = min(g, limit) and u' = clamp(u, -limit, limit):  g' * sigmoid(1.702 g') * (u' + 1)
+enum { SSB_GATE_SILU = 0, SSB_GATE_CLAMPED_SWISH = 1 };
+__device__ __forceinline__ float ssb_gate(float g, float u, int kind, float limit) {
+    if (kind == SSB_GATE_SILU) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 // Location of token `pos` of sequence slot `slot` in a paged cache entry laid out as
 // [page][kv_head][token_in_page][head_dim]; returns the element offset of the head's row.
 __device__ __forceinline__ size_t ssb_cache_row(const int* __restrict__ page_table, int max_pages,

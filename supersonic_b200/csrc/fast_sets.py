@@ -186,8 +186,11 @@ class FastKernels(PlainKernels):
         both = torch.stack([gate.view(inter // 8, 8, -1), up.view(inter // 8, 8, -1)], dim=1)
         return both.reshape(2 * inter, -1).contiguous(), "interleaved"      # [8 gate | 8 up] per 16 rows
 
-    def gate_up_swiglu(self, x, w_gate_up, layout, out):
+    def gate_up_swiglu(self, x, w_gate_up, layout, out, act=None, row_scale=None):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
+        if act is not None or row_scale is not None:
+            super().gate_up_swiglu(x, w_gate_up, layout, out, act, row_scale)
+            return
         if layout == "interleaved":
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
@@ -409,12 +412,12 @@ class FastKernels(PlainKernels):
                                       chunk, window, scale)
 
     def window_attention(self, q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool,
-                         scale, softcap, sinks, value_position, out_scale=1.0):
+                         scale, softcap, sinks, value_position, out_scale=1.0, v_share=1, gate=None):
         k_cache, v_cache, table, _ = kv
         pooled = None if pooled_kv is None else pooled_kv[:3]
         if not ops.window_attention_mma_ok(q, k_cache, v_cache, pooled, out, dim, vdim, page_shift):
             super().window_attention(q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first,
-                                     pool, scale, softcap, sinks, value_position, out_scale)
+                                     pool, scale, softcap, sinks, value_position, out_scale, v_share, gate)
             return
         vcos = vsin = None
         v_inter = False
@@ -423,7 +426,8 @@ class FastKernels(PlainKernels):
             v_inter = bool(getattr(value_position, "interleaved", False))
         ops.window_attention_mma(q, k_cache, v_cache, table, pooled, batch.cu_new, batch.seq_start, batch.seq_slot, out,
                                  batch.max_new, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool, scale, softcap,
-                                 sinks, vcos, vsin, v_inter, out_scale, pdl=self._chain(batch.n_tokens))
+                                 sinks, vcos, vsin, v_inter, out_scale, pdl=self._chain(batch.n_tokens), v_share=v_share,
+                                 gate=gate)
 
     def gated_linear_scan(self, proj, q_off, k_off, v_off, z, z_bias, tau, q_scale, state, batch, out, n_heads,
                           dim, vdim):
@@ -451,8 +455,10 @@ class FastKernels(PlainKernels):
         else:
             super().grouped_linear(a, gather, top, w, out, scatter, groups)
 
-    def expert_gate_up(self, x, top, w_gate_up, out, groups):
-        if ops.grouped_gemm_mma_ok(x, w_gate_up, out, ops.GG_SWIGLU):
+    def expert_gate_up(self, x, top, w_gate_up, out, groups, act=None):
+        if act is not None:
+            super().expert_gate_up(x, top, w_gate_up, out, groups, act)
+        elif ops.grouped_gemm_mma_ok(x, w_gate_up, out, ops.GG_SWIGLU):
             ops.grouped_gemm_mma(x, groups["order"], top, w_gate_up, out, None, groups["offsets"],
                                  groups["tile_expert"], groups["tile_row0"], groups["meta"], groups["max_tiles"],
                                  ops.GG_SWIGLU, pdl=self.pdl)

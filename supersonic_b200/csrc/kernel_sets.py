@@ -65,6 +65,9 @@ class PlainKernels:
     def embed(self, ids, table, out, scale=1.0):
         ops.embed(ids, table, out, scale)
 
+    def embed_norm(self, ids, table, weight, eps, out, scale=1.0):
+        ops.embed_norm(ids, table, weight, eps, out, scale)
+
     def rmsnorm(self, x, weight, eps, out, rows=None):
         ops.rmsnorm(x, weight, eps, out, rows)
 
@@ -76,12 +79,21 @@ class PlainKernels:
         """Gate and up weights as one matrix, in the layout ``gate_up_swiglu`` wants."""
         return torch.cat([gate, up], dim=0).contiguous(), "halves"
 
-    def gate_up_swiglu(self, x, w_gate_up, layout, out):
-        """out = silu(x @ gate^T) * (x @ up^T)."""
+    def gate_up_swiglu(self, x, w_gate_up, layout, out, act=None, row_scale=None):
+        """out = silu(x @ gate^T) * (x @ up^T); ``act`` = (kind, limit) names another inner step of the gated unit
+        (``ops.gated_activation``); ``row_scale``: one float32 factor per row of ``out``."""
         x = as_tensor(x)
         gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
         self.linear(x, w_gate_up, gate_up)
-        ops.swiglu(gate_up, out, interleaved=(layout == "interleaved"))
+        kind, limit = act if act else ("silu", 0.0)
+        ops.gated_activation(gate_up, out, kind, limit, interleaved=(layout == "interleaved"), row_scale=row_scale,
+                             pdl=self._chain(x.shape[0]))
+
+    def rms_add(self, residual, branch, weight, eps, clear=False, next_norm=None, next_out=None):
+        """residual += rmsnorm(branch) * weight; with ``next_norm`` (an RMS norm part) its output of the new stream
+        into ``next_out`` in the same pass."""
+        ops.rms_add(residual, branch, weight, eps, clear, None if next_norm is None else next_norm.weight_f32,
+                    0.0 if next_norm is None else next_norm.eps, next_out, pdl=self._chain(residual.shape[0]))
 
     def project_rope_append(self, x, w_qkv, qkv, position, kv, batch, n_q, n_kv, head_dim, page_shift) -> bool:
         """The q/k/v projection with position encoding and cache append in one kernel: rotated q
@@ -191,9 +203,9 @@ class PlainKernels:
         ops.tanh_norm_shift(x, norm1, norm2, mu, last, batch.cu_new, batch.seq_slot, mixed, second, batch.max_new,
                             pdl=self._chain(batch.n_tokens))
 
-    def causal_conv(self, x, x_bias, weight, bias, tail, batch, out):
+    def causal_conv(self, x, x_bias, weight, bias, tail, batch, out, pass_cols=0):
         ops.causal_conv(x, x_bias, weight, bias, tail, batch.cu_new, batch.seq_slot, out, batch.max_new,
-                        pdl=self._chain(batch.n_tokens))
+                        pdl=self._chain(batch.n_tokens), pass_cols=pass_cols)
 
     def concat_cast(self, x, x0, act, bias, out):
         ops.concat_cast(x, x0, act, bias, out, pdl=self._chain(x.shape[0]))
@@ -235,7 +247,7 @@ class PlainKernels:
         self.activation(u, out, kind, scale)
 
     def qkv_prepare(self, qkv, q_weight, k_weight, norm, eps, position, value_position, kv, batch, n_q, n_kv, dim, vdim,
-                    page_shift, write_cache=True, pooled_kv=None, pool=0) -> bool:
+                    page_shift, write_cache=True, pooled_kv=None, pool=0, v_off=None, q_temp=None, n_v=None) -> bool:
         """Norm of q and k (``norm`` ``"head"``, ``"row"`` or None), rotation of their first coordinates by
         ``position``, of the values over their whole width by ``value_position`` (either may be None), k and v into
         the cache.  With a pooled store and a step of one token a sequence, the tokens that end a run of ``pool``
@@ -254,7 +266,8 @@ class PlainKernels:
         k_cache, v_cache, table, _ = kv
         ops.qkv_prepare(qkv, q_weight, k_weight, norm, eps, cos, sin, rot_dims, inter, vcos, vsin, v_inter, batch.pos,
                         batch.slot_of_token, table, k_cache, v_cache, n_q, n_kv, dim, vdim, page_shift, write_cache,
-                        pdl=self._chain(batch.n_tokens), pooled=pooled_kv[:3] if pools else None, pool=pool if pools else 0)
+                        pdl=self._chain(batch.n_tokens), pooled=pooled_kv[:3] if pools else None, pool=pool if pools else 0,
+                        v_off=v_off, q_temp=q_temp, n_v=n_v)
         return pools
 
     def pool_rows(self, kv, pooled_kv, batch, n_kv, dim, vdim, page_shift, pool):
@@ -265,7 +278,7 @@ class PlainKernels:
                       batch.max_new, n_kv, dim, vdim, page_shift, pool, pdl=self._chain(batch.n_tokens))
 
     def window_attention(self, q, kv, pooled_kv, batch, out, n_q, n_kv, dim, vdim, page_shift, window, keep_first, pool,
-                         scale, softcap, sinks, value_position, out_scale=1.0):
+                         scale, softcap, sinks, value_position, out_scale=1.0, v_share=1, gate=None):
         vcos = vsin = None
         v_inter = False
         if value_position is not None:
@@ -275,7 +288,10 @@ class PlainKernels:
         pooled = None if pooled_kv is None else pooled_kv[:3]
         ops.window_attention_plain(q, k_cache, v_cache, table, pooled, batch.pos, batch.slot_of_token, out, n_q, n_kv,
                                    dim, vdim, page_shift, window, keep_first, pool, scale, softcap, sinks, vcos, vsin,
-                                   v_inter, out_scale, pdl=self._chain(batch.n_tokens))
+                                   v_inter, out_scale, pdl=self._chain(batch.n_tokens), v_share=v_share, gate=gate)
+
+    def map_difference(self, maps, out, n_heads, n_kv, vdim, lam, eps, mult):
+        ops.map_difference(maps, out, n_heads, n_kv, vdim, lam, eps, mult, pdl=self._chain(maps.shape[0]))
 
     def mingru_scan(self, proj, z_bias, x_bias, state, batch, out, width, out_scale=1.0):
         scratch = None
@@ -291,6 +307,11 @@ class PlainKernels:
     def route_table(self, token_ids, table, n_experts, expert_of, pair_weight):
         ops.route_table(token_ids, table, n_experts, expert_of, pair_weight)
 
+    def route_sigmoid_groups(self, x, weight, correction, extra_weight, n_groups, keep, scale, expert_of, pair_weight,
+                             extra_out=None):
+        ops.route_sigmoid_groups(x, weight, correction, extra_weight, n_groups, keep, scale, expert_of, pair_weight,
+                                 extra_out, pdl=self._chain(x.shape[0]))
+
     def group_by_expert(self, expert_of, n_experts, groups):
         """``groups``: the dict of int32 tensors a grouped product reads (offsets, order, tile_expert,
         tile_row0, meta) plus ``max_tiles``."""
@@ -304,12 +325,14 @@ class PlainKernels:
                                groups["order"] if scatter else None, groups["offsets"], groups["tile_expert"],
                                groups["tile_row0"], groups["meta"], groups["max_tiles"])
 
-    def expert_gate_up(self, x, top, w_gate_up, out, groups):
+    def expert_gate_up(self, x, top, w_gate_up, out, groups, act=None):
         """out[sorted row] = silu(x gate_e^T) * (x up_e^T) for the row's expert e; ``w_gate_up`` [E, 2 * inter,
-        hidden] holds gate rows, then up rows; ``x``'s rows are tokens (gathered through the order)."""
+        hidden] holds gate rows, then up rows; ``x``'s rows are tokens (gathered through the order).  ``act`` =
+        (kind, limit): another inner step of the gated unit."""
         gate_up = torch.empty((out.shape[0], w_gate_up.shape[1]), dtype=x.dtype, device=x.device)
         self.grouped_linear(x, True, top, w_gate_up, gate_up, False, groups)
-        ops.swiglu(gate_up, out)
+        kind, limit = act if act else ("silu", 0.0)
+        ops.gated_activation(gate_up, out, kind, limit, pdl=self._chain(out.shape[0]))
 
     def expert_combine(self, residual, y, pair_weight, top):
         ops.expert_combine(residual, y, pair_weight, top)

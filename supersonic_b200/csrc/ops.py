@@ -95,6 +95,19 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: floa
         c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale), _stream()), "embed")
 
 
+def embed_norm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+               scale: float = 1.0) -> None:
+    """out[t] = e / sqrt(mean(e^2) + eps) * weight with e = table[ids[t]] * scale, float32 (``weight`` float32)."""
+    _need(ids, "ids", torch.int32, 1); _need(table, "table", None, 2); _need(out, "out", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    if not (table.is_contiguous() and out.is_contiguous()) or out.shape[0] != ids.shape[0] \
+            or out.shape[1] != table.shape[1] or weight.shape[0] != table.shape[1]:
+        raise KernelError(f"embed_norm: out {tuple(out.shape)} does not fit {ids.shape[0]} ids of width {table.shape[1]}")
+    _check(_fn("plain_ops", "ssb_embed_norm")(
+        _ptr(ids), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(weight), c_float(eps), _ptr(out), c_int(ids.shape[0]),
+        c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale), _stream()), "embed_norm")
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
     """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight, x float32."""
@@ -210,6 +223,51 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) 
         _ptr(gate_up), c_int(gate_up.stride(0)), _ptr(out), c_int(out.stride(0)),
         c_int(dtype_code(out.dtype)), c_int(T), c_int(inter), c_int(1 if interleaved else 0),
         _stream()), "swiglu")
+
+
+GATE_KINDS_FF = {"silu": 0, "clamped_swish": 1}
+
+
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str = "silu", limit: float = 0.0,
+                     interleaved: bool = False, row_scale: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """out[t, c] = f(gate[t, c], up[t, c]) * row_scale[t] in float32 arithmetic.  ``kind`` ``"silu"``: silu(g) u;
+    ``"clamped_swish"``: with g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1).  Gate and up
+    are the halves of a row of ``gate_up``, or (interleaved) alternate as [8 gate | 8 up] per 16 columns."""
+    _need(gate_up, "gate_up", None, 2); _need(out, "out", gate_up.dtype, 2)
+    if kind not in GATE_KINDS_FF:
+        raise KernelError(f"gated_activation: kind {kind!r} is not known (known: {sorted(GATE_KINDS_FF)})")
+    T, inter = out.shape
+    if gate_up.shape[0] != T or gate_up.shape[1] != 2 * inter:
+        raise KernelError("gated_activation: gate_up must be [T, 2*I] for out [T, I]")
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32, 1)
+        if row_scale.shape[0] != T:
+            raise KernelError("gated_activation: one factor per row")
+    _check(_fn("plain_ops", "ssb_gated_activation")(
+        _ptr(gate_up), c_int(gate_up.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(T),
+        c_int(inter), c_int(1 if interleaved else 0), c_int(GATE_KINDS_FF[kind]), c_float(limit), _ptr(row_scale),
+        c_int(1 if pdl else 0), _stream()), "gated_activation")
+
+
+def rms_add(residual: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float, clear: bool = False,
+            next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None,
+            pdl: bool = False) -> None:
+    """residual[t] += branch[t] / sqrt(mean(branch[t]^2) + eps) * weight (both float32; ``weight`` is the multiplier
+    itself).  ``clear``: the branch is zeroed behind the read.  With ``next_out``: next_out[t] = the new residual[t]
+    / sqrt(mean(.^2) + next_eps) * next_weight, the norm the next sublayer reads."""
+    _need(residual, "residual", torch.float32, 2); _need(branch, "branch", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    T, W = residual.shape
+    if tuple(branch.shape) != (T, W) or weight.shape[0] != W or not (residual.is_contiguous() and branch.is_contiguous()):
+        raise KernelError("rms_add: residual and branch [tokens, width] contiguous, one weight per column")
+    if next_out is not None:
+        _need(next_out, "next_out", None, 2); _need(next_weight, "next_weight", torch.float32, 1)
+        if tuple(next_out.shape) != (T, W) or next_weight.shape[0] != W or not next_out.is_contiguous():
+            raise KernelError("rms_add: next_out [tokens, width] contiguous, one weight per column")
+    _check(_fn("plain_ops", "ssb_rms_add")(
+        _ptr(residual), _ptr(branch), _ptr(weight), c_float(eps), c_int(T), c_int(W), c_int(1 if clear else 0),
+        _ptr(next_weight if next_out is not None else None), c_float(next_eps), _ptr(next_out),
+        c_int(dtype_code(next_out.dtype) if next_out is not None else F32), c_int(1 if pdl else 0), _stream()), "rms_add")
 
 
 def add_into(out: torch.Tensor, x: torch.Tensor) -> None:
@@ -709,13 +767,14 @@ CONV_MAX_TAPS = 16
 
 def causal_conv(x: torch.Tensor, x_bias: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
                 tail: torch.Tensor, cu_new: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, max_new: int,
-                pdl: bool = False) -> None:
+                pdl: bool = False, pass_cols: int = 0) -> None:
     """out[t, c] = bias[c] + sum_j weight[c, j] * in[t - (taps - 1 - j), c] with in = x + x_bias; inputs from before
-    the step are ``tail[slot]`` ([taps - 1, channels] float32, oldest first), which is brought up to date."""
+    the step are ``tail[slot]`` ([taps - 1, channels] float32, oldest first), which is brought up to date.  The
+    ``pass_cols`` columns behind the channels are copied to ``out`` as they are."""
     _need(x, "x", None, 2); _need(weight, "weight", torch.float32, 2); _need(tail, "tail", torch.float32, 2)
     _need(out, "out", x.dtype, 2)
     C, taps = weight.shape
-    if taps > CONV_MAX_TAPS or x.shape[1] < C or out.shape[1] < C or out.shape[0] != x.shape[0] \
+    if taps > CONV_MAX_TAPS or x.shape[1] < C + pass_cols or out.shape[1] < C + pass_cols or out.shape[0] != x.shape[0] \
             or tail.shape[1] != (taps - 1) * C or not weight.is_contiguous() \
             or not tail.is_contiguous() or cu_new.shape[0] != seq_slot.shape[0] + 1:
         raise KernelError(f"causal_conv: shapes (up to {CONV_MAX_TAPS} taps)")
@@ -727,7 +786,7 @@ def causal_conv(x: torch.Tensor, x_bias: Optional[torch.Tensor], weight: torch.T
     _check(_fn("sequence_ops", "ssb_causal_conv")(
         _ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(x_bias), _ptr(weight), _ptr(bias), _ptr(tail),
         _ptr(cu_new), _ptr(seq_slot), _ptr(out), c_int(out.stride(0)), c_int(seq_slot.shape[0]), c_int(max_new),
-        c_int(C), c_int(taps), c_int(1 if pdl else 0), _stream()), "causal_conv")
+        c_int(C), c_int(taps), c_int(pass_cols), c_int(1 if pdl else 0), _stream()), "causal_conv")
 
 
 def concat_cast(x: torch.Tensor, x0: torch.Tensor, act: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -905,7 +964,7 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
                 v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_interleaved: bool, pos: torch.Tensor,
                 slot: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int,
                 n_kv: int, dim: int, vdim: int, page_shift: int, write_cache: bool = True, pdl: bool = False,
-                pooled=None, pool: int = 0) -> None:
+                pooled=None, pool: int = 0, v_off: Optional[int] = None, q_temp=None, n_v: Optional[int] = None) -> None:
     """Rows [q (n_q x dim) | k (n_kv x dim) | v (n_kv x vdim)].  ``norm`` ``"head"``: every q and k head is divided
     by its root mean square (eps inside the root) and multiplied by a weight vector [dim] shared by the heads;
     ``"row"``: all heads of q (of k) together are divided by one root mean square, weights [heads x dim]; None:
@@ -913,15 +972,24 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
     with ``v_cos``/``v_sin`` [positions, vdim / 2] every value head over its whole width.  q is written back in
     place; k and v go to the token's place in the paged cache.  ``pooled`` = (keys, values, page table) of a store
     with a row per run of ``pool`` tokens, only for steps that bring one token a sequence: the token that ends a
-    run writes the run's pooled row as ``pool_rows`` would."""
+    run writes the run's pooled row as ``pool_rows`` would.  ``v_off``: the column where the values start (default:
+    behind the keys; the keys' own column for values that are the keys as projected, before their norm).  ``q_temp`` =
+    (coef, every): the queries at position p are multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  ``n_v``:
+    value heads, if fewer than key heads (several score maps over the same values)."""
     _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     if norm not in QK_NORM_MODES:
         raise KernelError(f"qkv_prepare: norm {norm!r} is not known ('head', 'row' or None)")
     mode = QK_NORM_MODES[norm]
     T = qkv.shape[0]
-    if qkv.shape[1] < n_q * dim + (n_kv * (dim + vdim) if write_cache else 0) or pos.shape[0] != T or slot.shape[0] != T:
+    v_off = (n_q + n_kv) * dim if v_off is None else int(v_off)
+    n_v = n_kv if n_v is None else int(n_v)
+    need = max(n_q * dim + n_kv * dim, v_off + n_v * vdim) if write_cache else n_q * dim
+    if qkv.shape[1] < need or v_off < 0 or pos.shape[0] != T or slot.shape[0] != T:
         raise KernelError("qkv_prepare: rows are too narrow, or not one position and slot per token")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    if q_temp and every < 1:
+        raise KernelError("qkv_prepare: the query temperature's period must be at least one token")
     if mode:
         for w, heads in ((q_weight, n_q), (k_weight, n_kv)):
             _need(w, "norm weight", torch.float32, 1)
@@ -956,8 +1024,8 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
         c_int(1 if v_interleaved else 0), c_int(positions), _ptr(pos), _ptr(slot), _ptr(page_table),
         c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(dim), c_int(vdim),
         c_int(page_shift), c_int(1 if write_cache else 0), _ptr(pk), _ptr(pv), _ptr(ptable),
-        c_int(ptable.shape[1] if ptable is not None else 0), c_int(int(pool) if pool else 0), c_int(1 if pdl else 0),
-        _stream()), "qkv_prepare")
+        c_int(ptable.shape[1] if ptable is not None else 0), c_int(int(pool) if pool else 0), c_int(v_off), c_int(n_v),
+        c_float(coef), c_int(every), c_int(1 if pdl else 0), _stream()), "qkv_prepare")
 
 
 def pool_rows(k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor, pk_cache: torch.Tensor,
@@ -984,13 +1052,19 @@ def pool_rows(k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Te
 
 
 def _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim, window, keep_first, pool,
-                           sinks, v_cos, v_sin, what):
+                           sinks, v_cos, v_sin, what, v_share=1, gate=None):
     _need(q, "q", None, 2); _need(out, "out", q.dtype, 2); _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
     _need(page_table, "page_table", torch.int32, 2)
     T = q.shape[0]
     if out.shape[0] != T or out.shape[1] < n_q * vdim or q.shape[1] < n_q * dim or n_q % n_kv \
             or k_cache.shape[-1] != dim or v_cache.shape[-1] != vdim:
         raise KernelError(f"{what}: q/out/cache shapes")
+    if v_share < 1 or n_kv % v_share or (pool and v_share > 1):
+        raise KernelError(f"{what}: {n_kv} key heads do not share values {v_share} at a time (and not with pooled runs)")
+    if gate is not None:
+        _need(gate, "gate", q.dtype, 2)
+        if gate.shape[0] != T or gate.shape[1] < n_q:
+            raise KernelError(f"{what}: one gate per token and head")
     pk = pv = ptable = None
     if pool:
         if not window:
@@ -1013,15 +1087,19 @@ def window_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                            pooled, pos: torch.Tensor, slot: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, dim: int,
                            vdim: int, page_shift: int, window: Optional[int], keep_first: int, pool: int, scale: float,
                            softcap: Optional[float], sinks, v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor],
-                           v_interleaved: bool, out_scale: float = 1.0, pdl: bool = False) -> None:
+                           v_interleaved: bool, out_scale: float = 1.0, pdl: bool = False, v_share: int = 1,
+                           gate: Optional[torch.Tensor] = None) -> None:
     """Softmax attention of every token over its slot's cache: the keys j with pos - window < j <= pos, the first
     ``keep_first`` tokens, and (``pool`` > 0, ``pooled`` = (keys, values, page table) of the pooled store) the
     pooled row of every run of ``pool`` tokens that ends at or before pos - window.  Scores times ``scale``, then
     ``softcap * tanh(s / softcap)`` if a cap is given.  ``sinks``: None, True (a sink of score 0 in the
     denominator) or one float per query head.  With ``v_cos``/``v_sin`` the head's sum is turned back by the
-    token's position.  ``out`` is multiplied by ``out_scale``."""
+    token's position.  ``out`` is multiplied by ``out_scale``.  ``v_share``: that many key heads in a row read one
+    value head (the value store has n_kv / v_share heads).  ``gate`` [tokens, >= n_q]: head h of token t is
+    multiplied by sigmoid(gate[t, h])."""
     pk, pv, ptable, positions = _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim,
-                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention")
+                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention",
+                                                       v_share, gate)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     zero_sink = sinks is True
     _check(_fn("window_attention", "ssb_window_attention_plain")(
@@ -1031,8 +1109,8 @@ def window_attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         c_int(vdim), c_int(page_shift), c_int(int(window) if window else 0), c_int(int(keep_first or 0)),
         c_int(int(pool or 0)), c_float(scale), c_float(float(softcap) if softcap else 0.0),
         _ptr(None if (sinks is None or isinstance(sinks, bool)) else sinks), c_int(1 if zero_sink else 0), _ptr(v_cos),
-        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(1 if pdl else 0),
-        _stream()), "window_attention_plain")
+        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(v_share), _ptr(gate),
+        c_int(gate.stride(0) if gate is not None else 0), c_int(1 if pdl else 0), _stream()), "window_attention_plain")
 
 
 def window_attention_mma_ok(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pooled, out: torch.Tensor,
@@ -1052,7 +1130,8 @@ def window_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          max_new: int, n_q: int, n_kv: int, dim: int, vdim: int, page_shift: int, window: Optional[int],
                          keep_first: int, pool: int, scale: float, softcap: Optional[float], sinks,
                          v_cos: Optional[torch.Tensor], v_sin: Optional[torch.Tensor], v_interleaved: bool,
-                         out_scale: float = 1.0, split: Optional[bool] = None, pdl: bool = False) -> None:
+                         out_scale: float = 1.0, split: Optional[bool] = None, pdl: bool = False, v_share: int = 1,
+                         gate: Optional[torch.Tensor] = None) -> None:
     """``window_attention_plain`` on mma.sync for bfloat16: a block streams what a tile of (token, head of one kv
     group) rows can see once (pooled rows, kept first tokens, the window's pages); scores, weights and sums
     float32, the weights entering the second product as hi + lo bfloat16.  ``split`` (default: steps of one
@@ -1060,7 +1139,8 @@ def window_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     if not window_attention_mma_ok(q, k_cache, v_cache, pooled if pool else None, out, dim, vdim, page_shift):
         raise KernelError(f"window_attention_mma: dim {dim}, vdim {vdim} or operands not supported")
     pk, pv, ptable, positions = _window_attention_args(q, k_cache, v_cache, page_table, pooled, out, n_q, n_kv, dim, vdim,
-                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention_mma")
+                                                       window, keep_first, pool, sinks, v_cos, v_sin, "window_attention_mma",
+                                                       v_share, gate)
     _need(cu_new, "cu_new", torch.int32, 1); _need(seq_start, "seq_start", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
     B = seq_slot.shape[0]
     if cu_new.shape[0] != B + 1 or seq_start.shape[0] != B:
@@ -1074,8 +1154,24 @@ def window_attention_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         c_int(vdim), c_int(page_shift), c_int(int(window) if window else 0), c_int(int(keep_first or 0)),
         c_int(int(pool or 0)), c_float(scale), c_float(float(softcap) if softcap else 0.0),
         _ptr(None if (sinks is None or isinstance(sinks, bool)) else sinks), c_int(1 if sinks is True else 0), _ptr(v_cos),
-        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(1 if split else 0),
-        c_int(1 if pdl else 0), _stream()), "window_attention_mma")
+        _ptr(v_sin), c_int(1 if v_interleaved else 0), c_int(positions), c_float(out_scale), c_int(v_share), _ptr(gate),
+        c_int(gate.stride(0) if gate is not None else 0), c_int(1 if split else 0), c_int(1 if pdl else 0), _stream()),
+        "window_attention_mma")
+
+
+def map_difference(maps: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, vdim: int, lam: float, eps: float,
+                   mult: float, pdl: bool = False) -> None:
+    """Two score maps per head over the same values, the second taken off the first: with a1, a2 the maps' results of
+    head h, o = a1 - lam a2 and out[t, h] = o / sqrt(mean(o^2) + eps) * mult.  ``maps`` [tokens, 2 n_heads vdim] in
+    the order [kv head][map][head of the group][vdim]; ``out`` [tokens, n_heads vdim], heads in their own order."""
+    _need(maps, "maps", None, 2); _need(out, "out", maps.dtype, 2)
+    T = maps.shape[0]
+    if out.shape[0] != T or maps.shape[1] < 2 * n_heads * vdim or out.shape[1] < n_heads * vdim or n_heads % n_kv:
+        raise KernelError("map_difference: shapes")
+    _check(_fn("window_attention", "ssb_map_difference")(
+        _ptr(maps), c_int(maps.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(maps.dtype)), c_int(T),
+        c_int(n_heads), c_int(n_kv), c_int(vdim), c_float(lam), c_float(eps), c_float(mult), c_int(1 if pdl else 0),
+        _stream()), "map_difference")
 
 
 # ---- minGRU --------------------------------------------------------------------------------
@@ -1136,6 +1232,35 @@ def route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, ex
     _check(_fn("expert_ops", "ssb_route_table")(
         _ptr(token_ids), _ptr(table), c_int(table.shape[0]), c_int(top), c_int(n_experts), _ptr(expert_of),
         _ptr(pair_weight), c_int(T), c_int(1 if pdl else 0), _stream()), "route_table")
+
+
+def route_sigmoid_groups(x: torch.Tensor, weight: torch.Tensor, correction: Optional[torch.Tensor],
+                         extra_weight: Optional[torch.Tensor], n_groups: int, keep: int, scale: float,
+                         expert_of: torch.Tensor, pair_weight: torch.Tensor, extra_out: Optional[torch.Tensor] = None,
+                         pdl: bool = False) -> None:
+    """Per token: s = sigmoid(weight @ x) in float32; the ``top`` experts with the largest s + correction among the
+    experts of the ``keep`` best of ``n_groups`` equal groups of neighbours (a group's score: the sum of its two
+    largest s + correction); pair_weight = s * scale of the chosen.  ``extra_weight`` [1, width]: its sigmoid per
+    token into ``extra_out``."""
+    _need(x, "x", None, 2); _need(weight, "weight", torch.float32, 2)
+    _need(expert_of, "expert_of", torch.int32, 2); _need(pair_weight, "pair_weight", torch.float32, 2)
+    T, W = x.shape
+    E, top = weight.shape[0], expert_of.shape[1]
+    if weight.shape[1] != W or not weight.is_contiguous() or tuple(expert_of.shape) != (T, top) \
+            or tuple(pair_weight.shape) != (T, top) or not (expert_of.is_contiguous() and pair_weight.is_contiguous()):
+        raise KernelError("route_sigmoid_groups: weight [experts, width]; expert_of and pair_weight [tokens, top], contiguous")
+    if correction is not None:
+        _need(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != E:
+            raise KernelError("route_sigmoid_groups: one correction per expert")
+    if extra_weight is not None:
+        _need(extra_weight, "extra_weight", torch.float32); _need(extra_out, "extra_out", torch.float32, 1)
+        if extra_weight.numel() != W or not extra_weight.is_contiguous() or extra_out.shape[0] != T:
+            raise KernelError("route_sigmoid_groups: the extra row has the input's width, its result one number per token")
+    _check(_fn("expert_ops", "ssb_route_sigmoid_groups")(
+        _ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(weight), _ptr(correction), _ptr(extra_weight), c_int(T),
+        c_int(W), c_int(E), c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _ptr(expert_of), _ptr(pair_weight),
+        _ptr(extra_out if extra_weight is not None else None), c_int(1 if pdl else 0), _stream()), "route_sigmoid_groups")
 
 
 def expert_tiles_bound(n_pairs: int, n_experts: int, tile_rows: int) -> int:

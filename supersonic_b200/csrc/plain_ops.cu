@@ -50,6 +50,46 @@ SSB_API int ssb_embed_scaled(const int* ids, const void* table, int table_dtype,
     return ssb_launch_status();
 }
 
+// out[t, :] = e / sqrt(mean(e^2) + eps) * w with e = table[ids[t], :] * scale: an embedding whose rows pass an RMS
+// norm on their way into the stream (w float32, the multiplier itself).  One block per token, two passes over the row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+embed_norm_kernel(const int* __restrict__ ids, const T* __restrict__ table, const float* __restrict__ w, float eps,
+                  float* __restrict__ out, int hidden, int vocab, float scale) {
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* dst = out + (size_t)t * hidden;
+    const bool ok = id >= 0 && id < vocab;               // the host refuses other ids; never read out of range
+    const T* src = table + (size_t)(ok ? id : 0) * hidden;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += 256) {
+        const float v = ok ? ssb_to_float(src[c]) * scale : 0.f;
+        sq = fmaf(v, v, sq);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += red[i];
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += 256) dst[c] = ok ? ssb_to_float(src[c]) * scale * inv * w[c] : 0.f;
+}
+
+SSB_API int ssb_embed_norm(const int* ids, const void* table, int table_dtype, const float* w, float eps, float* out,
+                           int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (table_dtype == SSB_F32)
+        embed_norm_kernel<float><<<n_tokens, 256, 0, stream>>>(ids, (const float*)table, w, eps, out, hidden, vocab, scale);
+    else if (table_dtype == SSB_BF16)
+        embed_norm_kernel<bf16><<<n_tokens, 256, 0, stream>>>(ids, (const bf16*)table, w, eps, out, hidden, vocab, scale);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return ssb_launch_status();
+}
+
 SSB_API int ssb_embed(const int* ids, const void* table, int table_dtype, float* out, int n_tokens,
                       int hidden, int vocab, cudaStream_t stream) {
     return ssb_embed_scaled(ids, table, table_dtype, out, n_tokens, hidden, vocab, 1.0f, stream);
@@ -418,12 +458,16 @@ SSB_API int ssb_attention_plain(const void* q, int ldq, int dtype, const void* k
 }
 
 // ---------------------------------------------------------------------------------------
-// swiglu: z[t, c] = silu(gate[t, c]) * up[t, c].  Gate and up are the two halves of a row, or
-// (interleaved) come as [8 gate | 8 up] per 16 columns
+// A gated unit's inner step: z[t, c] = gate_fn(gate[t, c], up[t, c]) * row_scale[t] (ssb_gate: silu(g) u, or the
+// clamped form g' sigmoid(1.702 g') (u' + 1)).  Gate and up are the two halves of a row, or (interleaved) come as
+// [8 gate | 8 up] per 16 columns.  row_scale: one float32 factor per row, or none.
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ z, int ldz, int inter,
-                              size_t total, int interleaved) {
+__global__ void gated_activation_kernel(const T* __restrict__ gu, int ld, T* __restrict__ z, int ldz, int inter,
+                                        size_t total, int interleaved, int kind, float limit,
+                                        const float* __restrict__ row_scale) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
@@ -432,22 +476,113 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ 
     const int cu = interleaved ? cg + 8 : inter + c;
     const float g = ssb_to_float(gu[t * ld + cg]);
     const float u = ssb_to_float(gu[t * ld + cu]);
-    z[t * ldz + c] = ssb_from_float<T>(g / (1.0f + expf(-g)) * u);
+    const float r = row_scale ? row_scale[t] : 1.0f;
+    z[t * ldz + c] = ssb_from_float<T>(ssb_gate(g, u, kind, limit) * r);
+}
+
+SSB_API int ssb_gated_activation(const void* gate_up, int ld, void* z, int ldz, int dtype, int n_tokens, int inter,
+                                 int interleaved, int kind, float limit, const float* row_scale, int pdl,
+                                 cudaStream_t stream) {
+    if ((interleaved && inter % 8) || kind < 0 || kind > SSB_GATE_CLAMPED_SWISH) return SSB_ERR_BAD_SIZE;
+    const size_t total = (size_t)n_tokens * inter;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, pdl != 0, (const float*)gate_up,
+                        ld, (float*)z, ldz, inter, total, interleaved, kind, limit, row_scale);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(gated_activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, pdl != 0, (const bf16*)gate_up,
+                        ld, (bf16*)z, ldz, inter, total, interleaved, kind, limit, row_scale);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
 }
 
 SSB_API int ssb_swiglu(const void* gate_up, int ld, void* z, int ldz, int dtype, int n_tokens, int inter,
                        int interleaved, cudaStream_t stream) {
-    if (interleaved && inter % 8) return SSB_ERR_BAD_SIZE;
-    const size_t total = (size_t)n_tokens * inter;
-    if (total == 0) return 0;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == SSB_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, ld, (float*)z, ldz, inter, total, interleaved);
-    else if (dtype == SSB_BF16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, ld, (bf16*)z, ldz, inter, total, interleaved);
-    else
-        return SSB_ERR_BAD_DTYPE;
-    return ssb_launch_status();
+    return ssb_gated_activation(gate_up, ld, z, ldz, dtype, n_tokens, inter, interleaved, SSB_GATE_SILU, 0.f, nullptr, 0,
+                                stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// A sublayer's result joins the stream through a norm of its own:
+//     residual[t] += branch[t] / sqrt(mean(branch[t]^2) + eps) * w
+// (w float32, the multiplier itself: a weight stored around zero arrives as 1 + w).  Optionally the branch row is
+// zeroed behind the read, so that the next sublayer's products can add into it again, and optionally the norm
+// that the next sublayer reads is taken of the new stream in the same pass:
+//     next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + next_eps) * next_w.
+// One block per token, the row in shared memory, sums in a fixed order.
+// ---------------------------------------------------------------------------------------
+constexpr int RA_THREADS = 256;
+
+__device__ __forceinline__ float ra_block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < RA_THREADS / 32; ++w) s += red[w];
+    return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RA_THREADS)
+rms_add_kernel(float* __restrict__ residual, float* __restrict__ branch, const float* __restrict__ w, float eps, int width,
+               int clear, const float* __restrict__ next_w, float next_eps, T* __restrict__ next_out) {
+    extern __shared__ float ra_row[];
+    __shared__ float red[RA_THREADS / 32];
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const size_t t = blockIdx.x;
+    const int tid = threadIdx.x;
+    float* br = branch + t * width;
+    float* rr = residual + t * width;
+    float sq = 0.f;
+    for (int c = tid; c < width; c += RA_THREADS) {
+        const float v = br[c];
+        ra_row[c] = v;
+        sq = fmaf(v, v, sq);
+        if (clear) br[c] = 0.f;
+    }
+    const float inv = 1.0f / sqrtf(ra_block_sum(sq, red) / (float)width + eps);
+    float sq2 = 0.f;
+    for (int c = tid; c < width; c += RA_THREADS) {
+        const float v = rr[c] + ra_row[c] * inv * w[c];
+        rr[c] = v;
+        ra_row[c] = v;
+        sq2 = fmaf(v, v, sq2);
+    }
+    if (next_out == nullptr) return;
+    const float inv2 = 1.0f / sqrtf(ra_block_sum(sq2, red) / (float)width + next_eps);
+    for (int c = tid; c < width; c += RA_THREADS)
+        next_out[t * width + c] = ssb_from_float<T>(ra_row[c] * inv2 * next_w[c]);
+}
+
+SSB_API int ssb_rms_add(float* residual, float* branch, const float* w, float eps, int n_tokens, int width, int clear,
+                        const float* next_w, float next_eps, void* next_out, int next_dtype, int pdl, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (width <= 0 || (size_t)width * sizeof(float) > 200 * 1024 || (next_out != nullptr && next_w == nullptr))
+        return SSB_ERR_BAD_SIZE;
+    const size_t smem = (size_t)width * sizeof(float);
+    int rc;
+#define SSB_RA(TYPE)                                                                                                 \
+    {                                                                                                                \
+        auto kern = rms_add_kernel<TYPE>;                                                                            \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+        }                                                                                                            \
+        rc = ssb_launch(kern, dim3(n_tokens), dim3(RA_THREADS), smem, stream, pdl != 0, residual, branch, w, eps,    \
+                        width, clear, next_w, next_eps, (TYPE*)next_out);                                            \
+    }
+    if (next_out == nullptr || next_dtype == SSB_F32) SSB_RA(float)
+    else if (next_dtype == SSB_BF16) SSB_RA(bf16)
+    else return SSB_ERR_BAD_DTYPE;
+#undef SSB_RA
+    return rc ? rc : ssb_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------

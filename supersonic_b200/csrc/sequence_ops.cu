@@ -239,7 +239,8 @@ template <typename T>
 __global__ void __launch_bounds__(SEQ_THREADS)
 causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ x_bias, const float* __restrict__ w,
                    const float* __restrict__ bias, float* __restrict__ tail, const int* __restrict__ cu_new,
-                   const int* __restrict__ seq_slot, T* __restrict__ u, int ldu, int channels, int taps, int tile) {
+                   const int* __restrict__ seq_slot, T* __restrict__ u, int ldu, int channels, int taps, int tile,
+                   int pass_cols) {
     const int b = blockIdx.x;
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
@@ -249,7 +250,12 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ x
     const int lo = t0 + blockIdx.y * tile, hi = min(t1, lo + tile);
     if (lo >= hi) return;
     const int c = blockIdx.z * SEQ_THREADS + threadIdx.x;
-    if (c >= channels) return;
+    if (c >= channels) {
+        // columns behind the channels pass through unchanged (what shares the rows with the convolved part)
+        if (c < channels + pass_cols)
+            for (int t = lo; t < hi; ++t) u[(size_t)t * ldu + c] = x[(size_t)t * ldx + c];
+        return;
+    }
     const int back = taps - 1;
     float wj[CONV_MAX_TAPS], win[CONV_MAX_TAPS];      // win[j]: the input that tap j sees for the token at hand
     const float xb = x_bias ? x_bias[c] : 0.f, cb = bias ? bias[c] : 0.f;
@@ -293,19 +299,19 @@ causal_conv_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ x
 
 SSB_API int ssb_causal_conv(const void* x, int ldx, int dtype, const float* x_bias, const float* w, const float* bias,
                             float* tail, const int* cu_new, const int* seq_slot, void* u, int ldu, int n_seqs,
-                            int max_new, int channels, int taps, int pdl, cudaStream_t stream) {
+                            int max_new, int channels, int taps, int pass_cols, int pdl, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
-    if (channels <= 0 || taps < 1 || taps > CONV_MAX_TAPS) return SSB_ERR_BAD_SIZE;
+    if (channels <= 0 || taps < 1 || taps > CONV_MAX_TAPS || pass_cols < 0) return SSB_ERR_BAD_SIZE;
     const int tile = 32;                                  // at least taps - 1
-    const dim3 grid(n_seqs, (max_new + tile - 1) / tile, (channels + SEQ_THREADS - 1) / SEQ_THREADS);
+    const dim3 grid(n_seqs, (max_new + tile - 1) / tile, (channels + pass_cols + SEQ_THREADS - 1) / SEQ_THREADS);
     if (grid.y > 65535 || grid.z > 65535) return SSB_ERR_BAD_SIZE;
     int rc;
     if (dtype == SSB_F32)
         rc = ssb_launch(causal_conv_kernel<float>, grid, dim3(SEQ_THREADS), 0, stream, pdl != 0, (const float*)x, ldx,
-                        x_bias, w, bias, tail, cu_new, seq_slot, (float*)u, ldu, channels, taps, tile);
+                        x_bias, w, bias, tail, cu_new, seq_slot, (float*)u, ldu, channels, taps, tile, pass_cols);
     else if (dtype == SSB_BF16)
         rc = ssb_launch(causal_conv_kernel<bf16>, grid, dim3(SEQ_THREADS), 0, stream, pdl != 0, (const bf16*)x, ldx,
-                        x_bias, w, bias, tail, cu_new, seq_slot, (bf16*)u, ldu, channels, taps, tile);
+                        x_bias, w, bias, tail, cu_new, seq_slot, (bf16*)u, ldu, channels, taps, tile, pass_cols);
     else
         return SSB_ERR_BAD_DTYPE;
     return rc ? rc : ssb_launch_status();

@@ -74,6 +74,9 @@ __device__ __forceinline__ void wa_pair(int c, int dims, int interleaved, int& o
 //   rot_dims / 2]); v: all vdim coordinates turned (tables [positions, vdim / 2]) if v tables are given.
 // q is written back in place, k and v go to the token's row of the paged cache.  In a step that brings one token a
 // sequence, the token that ends a run of `pool` tokens may write the run's pooled row as well (see pool_rows).
+//   v_off: the column of the row where the values start (behind the keys; at the keys themselves for a mixer whose
+//   values are its keys as projected, before their norm).
+//   q_temp_every > 0: the queries of position p are multiplied by 1 + q_temp_coef * ln(floor((p + 1) / every) + 1).
 // ---------------------------------------------------------------------------------------
 constexpr int WP_THREADS = 256;
 
@@ -85,7 +88,8 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
                    int table_positions, const int* __restrict__ pos, const int* __restrict__ slot,
                    const int* __restrict__ page_table, int max_pages, T* __restrict__ k_cache, T* __restrict__ v_cache,
                    int n_q, int n_kv, int dim, int vdim, int page_shift, int write_cache, T* __restrict__ pk_cache,
-                   T* __restrict__ pv_cache, const int* __restrict__ pool_table, int pool_max_pages, int pool) {
+                   T* __restrict__ pv_cache, const int* __restrict__ pool_table, int pool_max_pages, int pool, int v_off,
+                   int n_v, float q_temp_coef, int q_temp_every) {
     extern __shared__ float wp_row[];                      // the part's row, then one factor per head
     __shared__ float red[WP_THREADS / 32];
     ssb_pdl_launch_dependents();
@@ -99,7 +103,7 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
     // pool > 0 (steps of one token a sequence only): the token that ends a run of `pool` tokens also writes the
     // run's pooled row, the mean of the cached rows in rising order (the other rows came with earlier steps, this
     // token's own was written by this block: the barrier orders it before the reads)
-    auto pool_run = [&](const T* cache, T* pooled, int width) {
+    auto pool_run = [&](const T* cache, T* pooled, int width) {      // pooled runs: as many value heads as key heads
         if (pool <= 0 || (p + 1) % pool) return;
         __syncthreads();
         const int run = p / pool;
@@ -113,8 +117,8 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
         }
     };
     if (part == 2) {
-        const T* src = base + (size_t)(n_q + n_kv) * dim;
-        const int n = n_kv * vdim;
+        const T* src = base + v_off;
+        const int n = n_v * vdim;                          // n_v value heads (fewer than key heads where several maps share them)
         const bool turn = vcos_t != nullptr && p < table_positions;
         for (int c = tid; c < n; c += WP_THREADS) wp_row[c] = ssb_to_float(src[c]);
         __syncthreads();
@@ -128,7 +132,7 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
                 const float cs = vcos_t[(size_t)p * (vdim >> 1) + pair], sn = vsin_t[(size_t)p * (vdim >> 1) + pair];
                 v = first ? v * cs - o * sn : v * cs + o * sn;
             }
-            v_cache[ssb_cache_row(page_table, max_pages, s, p, page_shift, n_kv, h, vdim) + d] = ssb_from_float<T>(v);
+            v_cache[ssb_cache_row(page_table, max_pages, s, p, page_shift, n_v, h, vdim) + d] = ssb_from_float<T>(v);
         }
         pool_run(v_cache, pv_cache, vdim);
         return;
@@ -165,9 +169,10 @@ qkv_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, c
     }
     __syncthreads();
     const bool turn = cos_t != nullptr && rot_dims > 0 && p < table_positions;
+    const float temp = (part == 0 && q_temp_every > 0) ? 1.0f + q_temp_coef * logf((float)((p + 1) / q_temp_every + 1)) : 1.0f;
     for (int c = tid; c < n; c += WP_THREADS) {
         const int h = c / dim, d = c - h * dim;
-        const float r = inv[h];
+        const float r = inv[h] * temp;
         const float* wr = norm_mode == 2 ? w + (size_t)h * dim : w;
         float v = wp_row[c] * r * (norm_mode ? wr[d] : 1.0f);
         if (turn && d < rot_dims) {
@@ -188,13 +193,17 @@ SSB_API int ssb_qkv_prepare(void* qkv, int ld, int dtype, const float* q_w, cons
                             const float* vsin_t, int v_interleaved, int table_positions, const int* pos, const int* slot,
                             const int* page_table, int max_pages, void* k_cache, void* v_cache, int n_tokens, int n_q,
                             int n_kv, int dim, int vdim, int page_shift, int write_cache, void* pk_cache, void* pv_cache,
-                            const int* pool_table, int pool_max_pages, int pool, int pdl, cudaStream_t stream) {
+                            const int* pool_table, int pool_max_pages, int pool, int v_off, int n_v, float q_temp_coef,
+                            int q_temp_every, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (dim <= 0 || vdim <= 0 || n_q <= 0 || n_kv <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) ||
+    if (v_off < 0) v_off = (n_q + n_kv) * dim;
+    if (n_v <= 0) n_v = n_kv;
+    if (n_v > n_kv || (pool > 0 && n_v != n_kv)) return SSB_ERR_BAD_SIZE;
+    if (dim <= 0 || vdim <= 0 || n_q <= 0 || n_kv <= 0 || q_temp_every < 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) ||
         norm_mode < 0 || norm_mode > 2 || (vcos_t != nullptr && (vdim & 1)) || pool < 0 ||
         (pool > 0 && (!write_cache || !pk_cache || !pv_cache || !pool_table)))
         return SSB_ERR_BAD_SIZE;
-    const int widest = max(n_q * dim, max(n_kv * dim, n_kv * vdim));
+    const int widest = max(n_q * dim, max(n_kv * dim, n_v * vdim));
     const size_t smem = ((size_t)widest + (size_t)max(n_q, n_kv)) * sizeof(float);
     if (smem > 200 * 1024) return SSB_ERR_BAD_SIZE;
     const dim3 grid(n_tokens, 3);
@@ -209,7 +218,8 @@ SSB_API int ssb_qkv_prepare(void* qkv, int ld, int dtype, const float* q_w, cons
         rc = ssb_launch(kern, grid, dim3(WP_THREADS), smem, stream, pdl != 0, (TYPE*)qkv, ld, q_w, k_w, norm_mode, eps,   \
                         cos_t, sin_t, rot_dims, interleaved, vcos_t, vsin_t, v_interleaved, table_positions, pos, slot,   \
                         page_table, max_pages, (TYPE*)k_cache, (TYPE*)v_cache, n_q, n_kv, dim, vdim, page_shift,          \
-                        write_cache, (TYPE*)pk_cache, (TYPE*)pv_cache, pool_table, pool_max_pages, pool);                 \
+                        write_cache, (TYPE*)pk_cache, (TYPE*)pv_cache, pool_table, pool_max_pages, pool, v_off, n_v,      \
+                        q_temp_coef, q_temp_every);                                                                       \
     }
     if (dtype == SSB_F32) SSB_WP(float)
     else if (dtype == SSB_BF16) SSB_WP(bf16)
@@ -300,7 +310,7 @@ window_attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restr
                               int n_q, int n_kv, int dim, int vdim, int page_shift, int window, int keep_first, int pool,
                               float scale, float softcap, const float* __restrict__ sinks, int zero_sink,
                               const float* __restrict__ vcos_t, const float* __restrict__ vsin_t, int v_interleaved,
-                              int table_positions, float out_scale) {
+                              int table_positions, float out_scale, int v_share, const T* __restrict__ gate, int ldg) {
     __shared__ float q_s[WA_MAX_DIM];
     __shared__ float p_s[WA_THREADS];
     __shared__ float red[WA_THREADS / 32];
@@ -315,7 +325,10 @@ window_attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restr
     }
     const int p = pos[t];
     const WaKeys keys = wa_keys_of(p, window, keep_first, pool);
-    const int kvh = h / (n_q / n_kv);
+    // v_share key heads in a row read the values of one value head (several score maps over the same values)
+    const int kvh = h / (n_q / n_kv), vh = kvh / v_share, n_v = n_kv / v_share;
+    // a gate per (token, head): the head's result is multiplied by sigmoid(gate)
+    const float gmul = (gate != nullptr ? 1.0f / (1.0f + expf(-ssb_to_float(gate[(size_t)t * ldg + h]))) : 1.0f) * out_scale;
     const T* qp = q + (size_t)t * ldq + (size_t)h * dim;
     for (int d = tid; d < dim; d += WA_THREADS) q_s[d] = ssb_to_float(qp[d]);
     __syncthreads();
@@ -324,13 +337,13 @@ window_attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restr
     auto rows_of = [&](int i, const T*& kr, const T*& vr) {
         if (i < keys.n_pool) {
             kr = pk_cache + ssb_cache_row(pool_table, pool_max_pages, s, i, page_shift, n_kv, kvh, dim);
-            vr = pv_cache + ssb_cache_row(pool_table, pool_max_pages, s, i, page_shift, n_kv, kvh, vdim);
+            vr = pv_cache + ssb_cache_row(pool_table, pool_max_pages, s, i, page_shift, n_v, vh, vdim);
             return;
         }
         i -= keys.n_pool;
         const int j = i < keys.n_keep ? i : keys.lo + (i - keys.n_keep);
         kr = k_cache + ssb_cache_row(page_table, max_pages, s, j, page_shift, n_kv, kvh, dim);
-        vr = v_cache + ssb_cache_row(page_table, max_pages, s, j, page_shift, n_kv, kvh, vdim);
+        vr = v_cache + ssb_cache_row(page_table, max_pages, s, j, page_shift, n_v, vh, vdim);
     };
 
     float m = -INFINITY, l = 0.f;
@@ -386,7 +399,7 @@ window_attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restr
 #pragma unroll
         for (int c = 0; c < WA_MAX_DIM / WA_THREADS; ++c) {
             const int d = tid + c * WA_THREADS;
-            if (d < vdim) o[d] = ssb_from_float<T>(acc[c] * inv * out_scale);
+            if (d < vdim) o[d] = ssb_from_float<T>(acc[c] * inv * gmul);
         }
         return;
     }
@@ -404,7 +417,7 @@ window_attention_plain_kernel(const T* __restrict__ q, int ldq, const T* __restr
         const float cs = vcos_t[(size_t)p * (vdim >> 1) + pair], sn = vsin_t[(size_t)p * (vdim >> 1) + pair];
         const float v = q_s[d], ov = q_s[other];
         const float r = first ? v * cs + ov * sn : v * cs - ov * sn;
-        o[d] = ssb_from_float<T>(r * out_scale);
+        o[d] = ssb_from_float<T>(r * gmul);
     }
 }
 
@@ -414,8 +427,10 @@ SSB_API int ssb_window_attention_plain(const void* q, int ldq, int dtype, const 
                                        int ldo, int n_tokens, int n_q, int n_kv, int dim, int vdim, int page_shift, int window,
                                        int keep_first, int pool, float scale, float softcap, const float* sinks,
                                        int zero_sink, const float* vcos_t, const float* vsin_t, int v_interleaved,
-                                       int table_positions, float out_scale, int pdl, cudaStream_t stream) {
+                                       int table_positions, float out_scale, int v_share, const void* gate, int ldg, int pdl,
+                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (v_share < 1 || n_kv % v_share) return SSB_ERR_BAD_SIZE;
     if (dim <= 0 || dim > WA_MAX_DIM || vdim <= 0 || vdim > WA_MAX_DIM || n_kv <= 0 || n_q % n_kv || n_q > 65535 ||
         window < 0 || keep_first < 0 || pool < 0 || (pool > 0 && (window <= 0 || pk_cache == nullptr || pool_table == nullptr)) ||
         (vcos_t != nullptr && (vdim & 1)))
@@ -427,13 +442,63 @@ SSB_API int ssb_window_attention_plain(const void* q, int ldq, int dtype, const 
                         (const float*)k_cache, (const float*)v_cache, page_table, max_pages, (const float*)pk_cache,
                         (const float*)pv_cache, pool_table, pool_max_pages, pos, slot, (float*)out, ldo, n_q, n_kv, dim, vdim,
                         page_shift, window, keep_first, pool, scale, softcap, sinks, zero_sink, vcos_t, vsin_t, v_interleaved,
-                        table_positions, out_scale);
+                        table_positions, out_scale, v_share, (const float*)gate, ldg);
     else if (dtype == SSB_BF16)
         rc = ssb_launch(window_attention_plain_kernel<bf16>, grid, dim3(WA_THREADS), 0, stream, pdl != 0, (const bf16*)q, ldq,
                         (const bf16*)k_cache, (const bf16*)v_cache, page_table, max_pages, (const bf16*)pk_cache,
                         (const bf16*)pv_cache, pool_table, pool_max_pages, pos, slot, (bf16*)out, ldo, n_q, n_kv, dim, vdim,
                         page_shift, window, keep_first, pool, scale, softcap, sinks, zero_sink, vcos_t, vsin_t, v_interleaved,
-                        table_positions, out_scale);
+                        table_positions, out_scale, v_share, (const bf16*)gate, ldg);
+    else
+        return SSB_ERR_BAD_DTYPE;
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// Two score maps per head over the same values, the second taken off the first:
+//     o = a1 - lambda * a2,   out = o / sqrt(mean(o^2) + eps) * mult     (mean over the head's vdim values)
+// The maps' results come in the order the attention kernels give them: [kv head][map][head of the group][vdim]
+// (a map's heads side by side, so that they share the map's keys); out is [head][vdim] with head = kv head * group
+// + head of the group.  One warp per (token, head); float32 throughout.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+map_difference_kernel(const T* __restrict__ maps, int ldm, T* __restrict__ out, int ldo, int n_tokens, int n_heads, int n_kv,
+                      int vdim, float lambda, float eps, float mult) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= (long long)n_tokens * n_heads) return;
+    const int t = (int)(w / n_heads), h = (int)(w % n_heads);
+    const int group = n_heads / n_kv, g = h / group, r = h - g * group;
+    const T* a1 = maps + (size_t)t * ldm + ((size_t)(g * 2) * group + r) * vdim;
+    const T* a2 = maps + (size_t)t * ldm + ((size_t)(g * 2 + 1) * group + r) * vdim;
+    float sq = 0.f;
+    for (int d = lane; d < vdim; d += 32) {
+        const float o = ssb_to_float(a1[d]) - lambda * ssb_to_float(a2[d]);
+        sq = fmaf(o, o, sq);
+    }
+    sq = wa_warp_sum(sq);
+    const float f = mult / sqrtf(sq / (float)vdim + eps);
+    T* op = out + (size_t)t * ldo + (size_t)h * vdim;
+    for (int d = lane; d < vdim; d += 32)
+        op[d] = ssb_from_float<T>((ssb_to_float(a1[d]) - lambda * ssb_to_float(a2[d])) * f);
+}
+
+SSB_API int ssb_map_difference(const void* maps, int ldm, void* out, int ldo, int dtype, int n_tokens, int n_heads, int n_kv,
+                               int vdim, float lambda, float eps, float mult, int pdl, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || vdim <= 0) return SSB_ERR_BAD_SIZE;
+    const long long warps = (long long)n_tokens * n_heads;
+    const dim3 grid((unsigned)((warps + 3) / 4));
+    int rc;
+    if (dtype == SSB_F32)
+        rc = ssb_launch(map_difference_kernel<float>, grid, dim3(128), 0, stream, pdl != 0, (const float*)maps, ldm, (float*)out,
+                        ldo, n_tokens, n_heads, n_kv, vdim, lambda, eps, mult);
+    else if (dtype == SSB_BF16)
+        rc = ssb_launch(map_difference_kernel<bf16>, grid, dim3(128), 0, stream, pdl != 0, (const bf16*)maps, ldm, (bf16*)out,
+                        ldo, n_tokens, n_heads, n_kv, vdim, lambda, eps, mult);
     else
         return SSB_ERR_BAD_DTYPE;
     return rc ? rc : ssb_launch_status();

@@ -41,6 +41,8 @@ struct WmArgs {
     const float* sinks; int zero_sink;
     const float* vcos; const float* vsin; int v_interleaved, table_positions;
     float out_scale;
+    int v_share;                  // key heads in a row that read the values of one value head (several score maps over the same values)
+    const bf16* gate; int ldg;    // one gate per (token, head), or none: the head's result is multiplied by sigmoid(gate)
 };
 
 template <int DIM, int VDIM, bool SPLIT, int ST>          // ST: pages in the ring
@@ -92,7 +94,7 @@ window_attention_mma_kernel(const WmArgs a) {
     auto load_tile = [&](int t, int stage, int id) {
         const bool pooled = t < t_pool;
         const bf16* ksrc = (pooled ? a.pk_cache : a.k_cache) + ((size_t)id * n_kv + kvh) * WM_PAGE * dim;
-        const bf16* vsrc = (pooled ? a.pv_cache : a.v_cache) + ((size_t)id * n_kv + kvh) * WM_PAGE * vdim;
+        const bf16* vsrc = (pooled ? a.pv_cache : a.v_cache) + ((size_t)id * (n_kv / a.v_share) + kvh / a.v_share) * WM_PAGE * vdim;
         bf16* kd = Ks + stage * WM_PAGE * KP;
         bf16* vd = Vs + stage * WM_PAGE * VP;
         // 16-byte pieces counted over the padded row (a power of two: shifts, no division); those past the real row are skipped
@@ -362,8 +364,10 @@ window_attention_mma_kernel(const WmArgs a) {
                 }
             }
         }
+        float mul = a.out_scale;
+        if (a.gate != nullptr) mul *= 1.0f / (1.0f + __expf(-__bfloat162float(a.gate[(size_t)(t0 + tok) * a.ldg + head])));
         bf16* o = a.out + (size_t)(t0 + tok) * a.ldo + (size_t)head * vdim + c;
-        *reinterpret_cast<uint32_t*>(o) = pack2(x0 * a.out_scale, x1 * a.out_scale);
+        *reinterpret_cast<uint32_t*>(o) = pack2(x0 * mul, x1 * mul);
     }
 }
 
@@ -393,9 +397,10 @@ SSB_API int ssb_window_attention_mma(const void* q, int ldq, const void* k_cache
                                      void* out, int ldo, int n_seqs, int max_new, int n_q, int n_kv, int dim, int vdim,
                                      int page_shift, int window, int keep_first, int pool, float scale, float softcap,
                                      const float* sinks, int zero_sink, const float* vcos_t, const float* vsin_t,
-                                     int v_interleaved, int table_positions, float out_scale, int split, int pdl,
-                                     cudaStream_t stream) {
+                                     int v_interleaved, int table_positions, float out_scale, int v_share, const void* gate,
+                                     int ldg, int split, int pdl, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (v_share < 1 || n_kv <= 0 || n_kv % v_share || (pool > 0 && v_share > 1)) return SSB_ERR_BAD_SIZE;
     if (page_shift != 6 || n_kv <= 0 || n_q % n_kv || (ldq & 1) || (ldo & 1) || window < 0 || keep_first < 0 || pool < 0 ||
         (pool > 0 && (window <= 0 || pk_cache == nullptr || pv_cache == nullptr || pool_table == nullptr)) ||
         dim <= 0 || vdim <= 0 || (dim & 7) || (vdim & 7))
@@ -414,6 +419,7 @@ SSB_API int ssb_window_attention_mma(const void* q, int ldq, const void* k_cache
     a.sinks = sinks; a.zero_sink = zero_sink;
     a.vcos = vcos_t; a.vsin = vsin_t; a.v_interleaved = v_interleaved; a.table_positions = table_positions;
     a.out_scale = out_scale;
+    a.v_share = v_share; a.gate = (const bf16*)gate; a.ldg = ldg;
     const int D = dim <= 64 ? 64 : 128, V = vdim <= 64 ? 64 : 128;
     const long long blocks = (long long)((max_new * (n_q / n_kv) + 15) / 16) * n_kv * n_seqs;     // of the decode form
     const bool deep = split && blocks <= WM_DEEP_MAX_BLOCKS;

@@ -1,5 +1,7 @@
 """Block arrangements.  ``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)),
 the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222).
+``sandwich``: h += norm_b(mixer(norm_a(h))); h += norm_d(feed_forward(norm_c(h))): a sublayer's result passes a
+norm of its own before it joins the stream.
 ``parallel``: h += mixer(n) + feed_forward(n) with the one n = norm(h), or with a norm each (both of the
 same h); optionally the mixer's input is mixed with the previous token's (token shift), and optionally the
 layer is followed by a learned weighted sum over the results of all layers so far."""
@@ -37,6 +39,58 @@ class PreNormBlock:
         x2 = NormedInput(ctx, residual, self.feed_forward_norm)
         ctx.stage = "feed_forward"
         self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """x <- x + norm_1b(mixer(norm_1(x))), then x <- x + norm_2b(feed_forward(norm_2(x))): RMS norms before and
+    behind each sublayer (the feed-forward may be absent).
+
+    ``params``: ``size``, ``eps``, ``unit_offset`` (the norms behind the sublayers multiply by 1 + w); tensors
+    ``mixer_out`` and ``feed_forward_out`` [size].  The sublayers add their products into a float32 row of zeros per
+    token (one buffer for the whole step, which the kernel that norms it and adds it to the stream zeroes again
+    behind its read); the same kernel takes the feed-forward's entry norm of the new stream, where that is an RMS
+    norm, so that between the two sublayers the stream is read once."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position, params=None, weights=None, build=None):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm, self.position = mixer_norm, feed_forward_norm, position
+        params, weights = params or {}, weights or {}
+        self.size, self.eps = int(params["size"]), float(params["eps"])
+        offset = 1.0 if params.get("unit_offset") else 0.0
+
+        def multiplier(role):
+            w = build.weights.stored(weights[role]).float()
+            if tuple(w.shape) != (self.size,):
+                raise ValueError(f"{weights[role]} has shape {tuple(w.shape)}, expected ({self.size},)")
+            return (w + offset).contiguous()
+        self.mixer_out = multiplier("mixer_out")
+        self.feed_forward_out = multiplier("feed_forward_out") if feed_forward is not None else None
+        self.dtype = build.dtype
+        self.fused_entry = feed_forward is not None and getattr(feed_forward_norm, "fusable_rms", False)
+
+    _give = staticmethod(PreNormBlock._give)
+
+    def forward(self, ctx, residual, cache_id, writes_cache):
+        branch = ctx.streams
+        if not (isinstance(branch, torch.Tensor) and branch.shape == residual.shape and branch.dtype == torch.float32):
+            branch = ctx.streams = torch.zeros_like(residual)         # zero again behind every use
+        x = NormedInput(ctx, residual, self.mixer_norm)
+        ctx.stage = "mixer"
+        self.mixer.forward(ctx, self._give(x, self.mixer), branch, cache_id, writes_cache, self.position)
+        if self.feed_forward is None:
+            ctx.kernels.rms_add(residual, branch, self.mixer_out, self.eps, clear=True)
+            return
+        ctx.stage = "feed_forward"
+        if self.fused_entry:
+            x2 = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+            ctx.kernels.rms_add(residual, branch, self.mixer_out, self.eps, clear=True, next_norm=self.feed_forward_norm,
+                                next_out=x2)
+        else:
+            ctx.kernels.rms_add(residual, branch, self.mixer_out, self.eps, clear=True)
+            x2 = self._give(NormedInput(ctx, residual, self.feed_forward_norm), self.feed_forward)
+        self.feed_forward.forward(ctx, x2, branch)
+        ctx.kernels.rms_add(residual, branch, self.feed_forward_out, self.eps, clear=True)
 
 
 @register_block("parallel")

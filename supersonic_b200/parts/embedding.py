@@ -11,12 +11,20 @@ from .registry import BuildContext, register_embedding
 
 @register_embedding("embedding")
 class Embedding:
-    """params: ``vocab_size``, ``hidden_size``, ``scale`` (optional: the rows are multiplied by it in float32);
-    weights: ``weight`` [vocab, hidden]."""
+    """params: ``vocab_size``, ``hidden_size``, ``scale`` (optional: the rows are multiplied by it in float32),
+    ``norm`` (optional, ``{"eps", "unit_offset"}``: the rows pass an RMS norm on their way into the stream, in the
+    same kernel); weights: ``weight`` [vocab, hidden], with a norm ``norm`` [hidden]."""
 
     def __init__(self, params, weights, build: BuildContext):
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
         self.scale = float(params.get("scale", 1.0))
+        self.norm_weight = None
+        if params.get("norm"):
+            w = build.weights.stored(weights["norm"]).float()
+            if tuple(w.shape) != (self.hidden,):
+                raise ValueError(f"{weights['norm']} has shape {tuple(w.shape)}, expected ({self.hidden},)")
+            self.norm_weight = (w + (1.0 if params["norm"].get("unit_offset") else 0.0)).contiguous()
+            self.norm_eps = float(params["norm"]["eps"])
         self.table = build.weights.as_dtype(weights["weight"], build.dtype, share=True)
         if tuple(self.table.shape) != (self.vocab, self.hidden):
             raise ValueError(f"{weights['weight']} has shape {tuple(self.table.shape)}, "
@@ -24,7 +32,10 @@ class Embedding:
 
     def __call__(self, ctx, token_ids):
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32, device=token_ids.device)
-        ctx.kernels.embed(token_ids, self.table, out, self.scale)
+        if self.norm_weight is not None:
+            ctx.kernels.embed_norm(token_ids, self.table, self.norm_weight, self.norm_eps, out, self.scale)
+        else:
+            ctx.kernels.embed(token_ids, self.table, out, self.scale)
         return out
 
 

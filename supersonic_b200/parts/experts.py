@@ -1,11 +1,18 @@
 """Feed-forward experts: y(x) = sum_k w_k E_(e_k)(x) over the ``top`` experts (e_k, w_k) a router picks for the
 token out of ``n_experts``, plus E_shared(x) if the layer has a shared expert.
 
-An expert is a gated unit without biases, E(x) = Wdown (silu(Wgate x) * (Wup x)).  Routers are registered
-by name and fill two arrays per step, the chosen experts and their weights:
+An expert is a gated unit without biases, E(x) = Wdown (silu(Wgate x) * (Wup x)), or with ``activation`` another
+inner step (see the ``swiglu`` feed-forward).  Routers are registered by name and fill two arrays per step, the
+chosen experts and their weights:
 
 * ``table``: nothing is learned and nothing is computed from x: row ``token id`` of an integer table
   [vocab, top] names the token's experts (distinct within a row), all with weight 1 / top.
+* ``sigmoid_groups``: scores s = sigmoid(W x) in float32; experts are chosen by s + correction (a stored vector),
+  but only among the experts of the ``keep`` best of ``groups`` equal groups of neighbours, a group's score being
+  the sum of its two largest choice scores; the weights are the chosen experts' s times ``scale``, not renormalized.
+
+A shared expert runs for every token; with ``shared.gate`` its result is multiplied by sigmoid(w_sg . x), one number
+per token.
 
 The step's (token, choice) pairs are sorted by expert on the device, the experts' matrix
 products run group by group from that order, and a token's outputs are summed in the order of
@@ -53,11 +60,44 @@ class TableRouter:
         ctx.kernels.route_table(ctx.batch.token_ids, self.table, self.n_experts, expert_of, pair_weight)
 
 
+@register_router("sigmoid_groups")
+class SigmoidGroupRouter:
+    """params: ``groups`` (1), ``keep`` (all groups), ``scale`` (1.0); weights: ``weight`` [experts, hidden],
+    ``correction`` [experts] (optional).  The logits are float32 sums over float32 copies of the stored weights.
+    ``extra`` (set by the part that owns the router): one more row whose sigmoid per token the router's kernel
+    writes along the way."""
+
+    def __init__(self, params, weights, build: BuildContext, n_experts: int, top: int):
+        self.n_experts, self.top = n_experts, top
+        self.groups = int(params.get("groups") or 1)
+        self.keep = int(params.get("keep") or self.groups)
+        self.scale = float(params.get("scale", 1.0))
+        if n_experts % self.groups or not 1 <= self.keep <= self.groups:
+            raise ValueError(f"sigmoid_groups: {n_experts} experts in {self.groups} groups, {self.keep} kept")
+        if top > self.keep * (n_experts // self.groups):
+            raise ValueError(f"sigmoid_groups: {top} experts a token cannot come from {self.keep} groups of "
+                             f"{n_experts // self.groups}")
+        self.weight = build.weights.stored(weights["weight"]).float().contiguous()
+        if self.weight.dim() != 2 or self.weight.shape[0] != n_experts:
+            raise ValueError(f"{weights['weight']} has shape {tuple(self.weight.shape)}, expected [{n_experts}, hidden]")
+        self.correction = None
+        if weights.get("correction"):
+            self.correction = build.weights.stored(weights["correction"]).float().contiguous()
+            if tuple(self.correction.shape) != (n_experts,):
+                raise ValueError(f"{weights['correction']} has shape {tuple(self.correction.shape)}, expected ({n_experts},)")
+        self.extra = None
+
+    def route(self, ctx, x, expert_of, pair_weight, extra_out=None):
+        ctx.kernels.route_sigmoid_groups(x, self.weight, self.correction, self.extra if extra_out is not None else None,
+                                         self.groups, self.keep, self.scale, expert_of, pair_weight, extra_out)
+
+
 @register_feed_forward("experts")
 class Experts:
-    """params: ``hidden_size``, ``n_experts``, ``top``, ``expert_size``, ``router`` ({"kind": ..., its own
-    parameters}), ``shared`` (None or {"intermediate_size": ...}); weights: ``gate.<e>``, ``up.<e>``,
-    ``down.<e>`` for every expert e, the router's own, and ``shared.gate`` / ``shared.up`` / ``shared.down``."""
+    """params: ``hidden_size``, ``n_experts``, ``top``, ``expert_size``, ``activation`` (None, or as the ``swiglu``
+    feed-forward's), ``router`` ({"kind": ..., its own parameters}), ``shared`` (None or {"intermediate_size": ...,
+    "activation": ..., "gate": bool}); weights: ``gate.<e>``, ``up.<e>``, ``down.<e>`` for every expert e, the router's
+    own, and ``shared.gate`` / ``shared.up`` / ``shared.down`` (with a gate ``shared.sg`` [1, hidden])."""
 
     takes_lazy_input = True
 
@@ -80,11 +120,22 @@ class Experts:
         if router.get("kind") not in ROUTERS:
             raise KeyError(f"unknown router {router.get('kind')!r}; registered: {sorted(ROUTERS)}")
         self.router = ROUTERS[router["kind"]](router, weights, build, self.E, self.top)
-        self.shared = None
+        from .feed_forward import SwiGLU, gated_activation_of
+        self.act = gated_activation_of(params.get("activation"))
+        self.shared, self.shared_gate = None, None
         if params.get("shared"):
-            from .feed_forward import SwiGLU
-            self.shared = SwiGLU({"hidden_size": self.hidden, "intermediate_size": int(params["shared"]["intermediate_size"])},
+            sh = params["shared"]
+            self.shared = SwiGLU({"hidden_size": self.hidden, "intermediate_size": int(sh["intermediate_size"]),
+                                  "activation": sh.get("activation")},
                                  {r: weights[f"shared.{r}"] for r in ("gate", "up", "down")}, build)
+            if sh.get("gate"):
+                sg = w.stored(weights["shared.sg"]).float().reshape(-1).contiguous()
+                if sg.numel() != self.hidden:
+                    raise ValueError(f"{weights['shared.sg']} has {sg.numel()} values, expected {self.hidden}")
+                if not hasattr(self.router, "extra"):
+                    raise ValueError(f"experts: the router {router['kind']!r} reads no activations, so it cannot take the "
+                                     "shared expert's gate along")
+                self.shared_gate = self.router.extra = sg     # the router's kernel reads the token anyway: it takes this row too
         self.dtype = dt
 
     @staticmethod
@@ -100,7 +151,12 @@ class Experts:
         P = T * top
         expert_of = torch.empty((T, top), dtype=torch.int32, device=dev)
         pair_weight = torch.empty((T, top), dtype=torch.float32, device=dev)
-        self.router.route(ctx, xt, expert_of, pair_weight)
+        shared_scale = None
+        if self.shared_gate is not None:
+            shared_scale = torch.empty(T, dtype=torch.float32, device=dev)
+            self.router.route(ctx, xt, expert_of, pair_weight, extra_out=shared_scale)
+        else:
+            self.router.route(ctx, xt, expert_of, pair_weight)
         tile_rows = ctx.kernels.expert_tile_rows
         max_tiles = P // tile_rows + min(self.E, P)
         ints = torch.empty(self.E + 1 + P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
@@ -110,9 +166,15 @@ class Experts:
                   "tile_row0": ints[self.E + 1 + P + max_tiles: self.E + 1 + P + 2 * max_tiles], "meta": ints[-1:]}
         ctx.kernels.group_by_expert(expert_of, self.E, groups)
         z = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
-        ctx.kernels.expert_gate_up(xt, top, self.w_gate_up, z, groups)
+        if self.act is None:
+            ctx.kernels.expert_gate_up(xt, top, self.w_gate_up, z, groups)
+        else:
+            ctx.kernels.expert_gate_up(xt, top, self.w_gate_up, z, groups, act=self.act)
         y = torch.empty((P, self.hidden), dtype=torch.float32, device=dev)
         ctx.kernels.grouped_linear(z, False, top, self.w_down, y, True, groups)
         ctx.kernels.expert_combine(residual, y, pair_weight, top)
         if self.shared is not None:
-            self.shared.forward(ctx, x, residual)
+            if shared_scale is None:
+                self.shared.forward(ctx, x, residual)
+            else:
+                self.shared.forward(ctx, x, residual, row_scale=shared_scale)

@@ -32,6 +32,13 @@ class RMSNorm:
             raise ValueError(f"rmsnorm weight has shape {tuple(self.weight.shape)}, expected ({self.size},)")
         self.dtype = build.dtype
 
+    @property
+    def weight_f32(self):
+        """The multiplier in float32, for kernels that take this norm inside another operation."""
+        if getattr(self, "_weight_f32", None) is None:
+            self._weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
+        return self._weight_f32
+
     def __call__(self, ctx, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
