@@ -364,6 +364,39 @@ def _ronelorn_sizes(name):
     return ron, vuf
 
 
+def _kilisun_sizes(name):
+    """(Kilisun config.json, the Ronelorn configuration of the same width, layer count and vocabulary: the closest
+    existing design for the mixers, whose window attention runs on the same kernels).  A differential window layer
+    with a dense feed-forward, a layer of attention over convolved keys that are its values, a second differential
+    layer and one that reads that layer's keys with a longer window, the last three with experts (sizes as the
+    Sotavik comparison's, whose expert products are the like kernels)."""
+    def diff(heads, kv, dim, vdim, window, kv_from=None):
+        m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": 30.0, "diff": 0.5,
+             "mask": {"size": window}, "rot": {"base": 10000.0, "dims": dim}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention_2", "mixer": m}
+
+    def conv(heads, kv, dim):
+        return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                               "conv": 4, "q_temp": {"coef": 0.1, "every": 1024}}}
+
+    def moe(experts, top, groups, keep, ff, shared):
+        return {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared, "limit": 7.0},
+                "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+    ron, _ = _ronelorn_sizes(name)
+    width, ff = ron["width"], ron["layers"][0]["mlp"]["ff"]
+    if name == "2048":
+        mixers = [diff(16, 4, 64, 128, 512), conv(16, 4, 128), diff(16, 4, 64, 128, 512), diff(16, 4, 64, 128, 1024, kv_from=2)]
+        experts = moe(64, 6, 8, 4, 1408, 2816)
+    else:
+        mixers = [diff(8, 2, 64, 128, 256), conv(8, 2, 128), diff(8, 2, 64, 128, 256), diff(8, 2, 64, 128, 512, kv_from=2)]
+        experts = moe(16, 2, 4, 2, 512, 1024)
+    layers = [dict(mixers[0], mlp={"kind": "dense", "ff": ff, "limit": 7.0})] + [dict(m, mlp=experts) for m in mixers[1:]]
+    kil = {"architecture": "Kilisun", "vocab": ron["vocab"], "width": width, "norm": {"eps": 1e-5}, "layers": layers}
+    return kil, ron
+
+
 def _operation_work(model, tokens):
     """Algorithmic work of one prompt of ``tokens`` tokens per operation of the model's parts: (FLOPs, bytes).
     Matrix products count 2 per multiply-add; attention counts its scores and weighted sums over the causal
@@ -410,12 +443,20 @@ def _operation_work(model, tokens):
                     add("mixer.linear", 2 * T * (sum(w.numel() for w in half.w) + half.w2.numel() + half.w_o.numel()))
                     add("mixer.matrix_state_scan", 6 * T * HD * half.dim, T * HD * (3 * 2 + 4 + 4))
         elif kind == "WindowAttention":
-            add("mixer.linear", 2 * T * (m.w_qkv.numel() + m.w_o.numel()))
+            maps = getattr(m, "maps", 1)
+            w_in = m.w_qkv if getattr(m, "own_kv", True) else m._read_weight()
+            add("mixer.linear", 2 * T * (w_in.numel() + m.w_o.numel()))
             w = int(m.window or T)
             pairs = sum(min(i + 1, w) + (max(0, i - w + 1) // m.pool if m.pool else min(m.keep_first, max(0, i - w + 1)))
                         for i in range(T))
-            add("mixer.window_attention", 2 * pairs * m.n_q * (m.dim + m.vdim))
-            add("mixer.qkv_prepare", 0, T * (m.n_q * m.dim * 4 + m.n_kv * (m.dim + m.vdim) * 4))
+            add("mixer.window_attention", 2 * pairs * m.n_q * maps * (m.dim + m.vdim))
+            kv_rows = m.n_kv * (maps * m.dim + m.vdim) if getattr(m, "own_kv", True) else 0
+            add("mixer.qkv_prepare", 0, T * (m.n_q * maps * m.dim * 4 + kv_rows * 4))
+            if getattr(m, "taps", 0):
+                C = m.conv_w.shape[0]
+                add("mixer.causal_conv", 2 * T * C * m.taps, T * w_in.shape[0] * 4)
+            if maps > 1:
+                add("mixer.map_difference", 0, T * m.n_q * m.vdim * (2 * maps + 2))
         elif kind == "MinGRU":
             add("mixer.linear", 2 * T * (m.w_in.numel() + m.w_o.numel()))
             add("mixer.mingru_scan", 10 * T * m.C, T * m.C * (3 * 2 + 2))                # z, x, g in; the gated state out
@@ -424,10 +465,16 @@ def _operation_work(model, tokens):
             add("mixer.project_rope_append", 2 * T * m.w_qkv.numel())
             add("mixer.attention", 4 * causal * m.n_q * m.head_dim)
         fk = type(ff).__name__ if ff is not None else ""
+        if type(b).__name__ == "SandwichBlock":
+            # behind each sublayer: the float32 branch in, zeros back, the stream in and out; once with the next norm's rows out
+            W = model.spec.hidden_size
+            add("feed_forward.rms_add", 0, T * W * ((4 * 4 + 2) + (4 * 4 if ff is not None else 0)))
         if fk == "Experts":
             per = ff.w_gate_up[0].numel() + ff.w_down[0].numel()
             add("feed_forward.expert_gate_up", 2 * T * ff.top * ff.w_gate_up[0].numel())
             add("feed_forward.grouped_linear", 2 * T * ff.top * ff.w_down[0].numel())
+            if getattr(getattr(ff.router, "weight", None), "dim", lambda: 0)() == 2:   # a router that reads the token: a product of its own
+                add("feed_forward.linear", 2 * T * ff.router.weight.numel())
             if ff.shared is not None:
                 add("feed_forward.gate_up_swiglu", 2 * T * ff.shared.w_gate_up.numel())
                 add("feed_forward.linear", 2 * T * ff.shared.w_down.numel())
@@ -449,15 +496,19 @@ def design_comparison(args):
     from supersonic_b200.engine import Model, StepEntry
     from supersonic_b200.weights import RandomWeightStore
     pk, pk_src = peaks()
-    sizes = {"vufadra": _vufadra_sizes, "sotavik": _sotavik_sizes, "ronelorn": _ronelorn_sizes}[args.design]
+    sizes = {"vufadra": _vufadra_sizes, "sotavik": _sotavik_sizes, "ronelorn": _ronelorn_sizes,
+             "kilisun": _kilisun_sizes}[args.design]
     sot, lla = sizes(args.design_size)
-    beside = "vufadra" if args.design == "ronelorn" else "llama"
+    beside = {"ronelorn": "vufadra", "kilisun": "ronelorn"}.get(args.design, "llama")
+    models = [(args.design, sot), (beside, lla)]
+    if args.design == "kilisun":                              # its experts beside the design whose expert products they run on
+        models.append(("sotavik", _sotavik_sizes(args.design_size)[0]))
     out = {"metric": "design_comparison", "design": args.design, "beside": beside, "size": args.design_size,
            "layers": len(sot["layers"]), "dtype": "bf16", "data": "synthetic", "peaks": pk, "peaks_source": pk_src,
            "models": {}}
     clocks = ClockSampler()
     clocks.start()
-    for name, d in ((args.design, sot), (beside, lla)):
+    for name, d in models:
         cfg = config_from_dict(d)
         store = RandomWeightStore(cfg, seed=3, device="cuda:0", std=0.02, norm_jitter=0.0)
         ctx = max(args.prefill_tokens, args.prompt_len) + 256
@@ -625,7 +676,7 @@ def main():
                     help="also time decode and prompts at further sizes (adds a 'sweep' key to the line)")
     ap.add_argument("--deterministic", action="store_true",
                     help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
-    ap.add_argument("--design", default=None, choices=["sotavik", "vufadra", "ronelorn"],
+    ap.add_argument("--design", default=None, choices=["sotavik", "vufadra", "ronelorn", "kilisun"],
                     help="instead of the headline workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="2048", help="width of the compared models: 1024 or 2048")
     args = ap.parse_args()

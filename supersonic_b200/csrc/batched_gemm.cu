@@ -30,6 +30,7 @@ struct BgArgs {
     const int* offsets; const int* tile_expert; const int* tile_row0; const int* meta;   // grouped form, else null
     int M, N, K;                                  // M: rows (per-head form); N: output columns; K
     int up_row0;                                  // SwiGLU: first row of the up half in a matrix
+    int gate_kind; float gate_limit;              // SwiGLU: the gated unit's inner step (ssb_gate_fast) and its clamp
 };
 
 template <bool SWIGLU, typename TC, int BG_STAGES, int BG_BK>
@@ -149,7 +150,7 @@ batched_gemm_kernel(const BgArgs g) {
                     float v = acc[0][i][j][hrow * 2 + x];
                     if (SWIGLU) {
                         const float u = acc[SWIGLU ? 1 : 0][i][j][hrow * 2 + x];
-                        v = v / (1.0f + __expf(-v)) * u;
+                        v = ssb_gate_fast(v, u, g.gate_kind, g.gate_limit);
                     }
                     C[crow * g.ldc + n] = ssb_from_float<TC>(v);
                 }
@@ -200,15 +201,18 @@ SSB_API int ssb_head_gemm_mma(const void* A, int lda, long long a_batch, const v
 SSB_API int ssb_grouped_gemm_mma(const void* A, int lda, const int* a_index, int a_div, const void* W, int ldw,
                                  long long w_expert, void* C, int ldc, const int* c_index, int out_dtype,
                                  const int* offsets, const int* tile_expert, const int* tile_row0, const int* meta,
-                                 int max_tiles, int n_rows, int N, int K, int mode, int pdl, cudaStream_t stream) {
-    // n_rows: the rows of all groups together (what the host knows of their sizes)
+                                 int max_tiles, int n_rows, int N, int K, int mode, int gate_kind, float gate_limit, int pdl,
+                                 cudaStream_t stream) {
+    // n_rows: the rows of all groups together (what the host knows of their sizes); gate_kind, gate_limit: the
+    // gated unit's inner step in mode 1 (0: silu(g) u)
     if (max_tiles <= 0 || N <= 0) return 0;
-    if (a_div <= 0) return SSB_ERR_BAD_SIZE;
+    if (a_div <= 0 || gate_kind < 0 || gate_kind > SSB_GATE_CLAMPED_SWISH) return SSB_ERR_BAD_SIZE;
     BgArgs a = {};
     a.A = (const bf16*)A; a.lda = lda; a.a_batch = 0; a.a_index = a_index; a.a_div = a_div;
     a.W = (const bf16*)W; a.ldw = ldw; a.w_batch = w_expert;
     a.C = C; a.ldc = ldc; a.c_batch = 0; a.c_index = c_index;
     a.offsets = offsets; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.meta = meta;
     a.M = 0; a.N = N; a.K = K; a.up_row0 = N;
+    a.gate_kind = gate_kind; a.gate_limit = gate_limit;
     return bg_launch(a, mode, out_dtype, dim3((N + BG_BN - 1) / BG_BN, max_tiles, 1), n_rows <= 1024, pdl, stream);
 }

@@ -53,6 +53,14 @@ __device__ __forceinline__ float ssb_gate(float g, float u, int kind, float limi
     return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
 }
 
+// The same where a product finishes its float32 sums (fast exponential: the result is rounded to bfloat16 next).
+__device__ __forceinline__ float ssb_gate_fast(float g, float u, int kind, float limit) {
+    if (kind == SSB_GATE_SILU) return __fdividef(g, 1.0f + __expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+}
+
 // Location of token `pos` of sequence slot `slot` in a paged cache entry laid out as
 // [page][kv_head][token_in_page][head_dim]; returns the element offset of the head's row.
 __device__ __forceinline__ size_t ssb_cache_row(const int* __restrict__ page_table, int max_pages,

@@ -41,46 +41,40 @@ SSB_API int ssb_route_table(const int* token_ids, const int* table, int vocab, i
 }
 
 // ---------------------------------------------------------------------------------------
-// sigmoid router with groups: z = W x in float32, s = sigmoid(z); an expert is chosen by s + correction among the
-// experts of the `keep` best groups (the experts form `n_groups` equal groups of neighbours; a group's score is
-// the sum of its two largest choice scores; the other groups' experts count as minus infinity); the `top` largest
-// choice scores win, the lower index at equal scores; an expert's weight is its s (without the correction) times
-// `scale`, not renormalized.  extra_w (or none): one more row; its sigmoid goes to extra_out[t] (the gate of a
-// shared expert).  One block per token: the warps take the dot products, one thread the choice.
+// sigmoid router with groups.  The logits z [tokens, ld] are float32 (a product of their own); s = sigmoid(z); an
+// expert is chosen by s + correction among the experts of the `keep` best groups (the experts form `n_groups` equal
+// groups of neighbours; a group's score is the sum of its two largest choice scores; the other groups' experts
+// count as minus infinity); the `top` largest choice scores win, the lower index at equal scores; an expert's weight
+// is its s (without the correction) times `scale`, not renormalized.  extra_col >= 0: the sigmoid of that column goes
+// to extra_out[t] (the gate of a shared expert, whose row rides along in the product).  One warp per token: lanes
+// over experts for the scores and for every pick, lanes over groups for the groups' scores.
 // ---------------------------------------------------------------------------------------
 constexpr int RG_THREADS = 128;
 
-template <typename T>
 __global__ void __launch_bounds__(RG_THREADS)
-route_sigmoid_groups_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ correction,
-                            const float* __restrict__ extra_w, int width, int n_experts, int n_groups, int keep, int top,
-                            float scale, int* __restrict__ expert_of, float* __restrict__ pair_weight,
-                            float* __restrict__ extra_out) {
-    extern __shared__ float rg_smem[];                   // [n_experts] s, [n_experts] choice, [n_groups] group scores
-    float* s_s = rg_smem;
-    float* c_s = rg_smem + n_experts;
-    float* g_s = c_s + n_experts;
+route_sigmoid_groups_kernel(const float* __restrict__ z, int ld, const float* __restrict__ correction, int n_tokens,
+                            int n_experts, int n_groups, int keep, int top, float scale, int extra_col,
+                            int* __restrict__ expert_of, float* __restrict__ pair_weight, float* __restrict__ extra_out) {
+    extern __shared__ float rg_smem[];                   // per warp: [n_experts] s, [n_experts] choice, [n_groups] group scores
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* xr = x + (size_t)t * ldx;
-    for (int e = warp; e < n_experts + (extra_w != nullptr ? 1 : 0); e += RG_THREADS / 32) {
-        const float* wr = e < n_experts ? w + (size_t)e * width : extra_w;
-        float dot = 0.f;
-        for (int c = lane; c < width; c += 32) dot = fmaf(ssb_to_float(xr[c]), wr[c], dot);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (lane == 0) {
-            const float sg = 1.0f / (1.0f + expf(-dot));
-            if (e < n_experts) { s_s[e] = sg; c_s[e] = sg + (correction ? correction[e] : 0.f); }
-            else extra_out[t] = sg;
-        }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (RG_THREADS / 32) + warp;
+    if (t >= n_tokens) return;
+    float* s_s = rg_smem + (size_t)warp * (2 * n_experts + n_groups);
+    float* c_s = s_s + n_experts;
+    float* g_s = c_s + n_experts;
+    const float* zr = z + (size_t)t * ld;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float sg = 1.0f / (1.0f + expf(-zr[e]));
+        s_s[e] = sg;
+        c_s[e] = sg + (correction ? correction[e] : 0.f);
     }
-    __syncthreads();
-    if (threadIdx.x != 0) return;
+    if (extra_col >= 0 && lane == 0) extra_out[t] = 1.0f / (1.0f + expf(-zr[extra_col]));
+    __syncwarp();
     const int per = n_experts / n_groups;
     if (keep < n_groups) {
-        for (int g = 0; g < n_groups; ++g) {
+        for (int g = lane; g < n_groups; g += 32) {
             float a = -INFINITY, b = -INFINITY;           // the two largest of the group
             for (int e = g * per; e < (g + 1) * per; ++e) {
                 const float v = c_s[e];
@@ -88,57 +82,62 @@ route_sigmoid_groups_kernel(const T* __restrict__ x, int ldx, const float* __res
             }
             g_s[g] = per > 1 ? a + b : a;
         }
+        __syncwarp();
         // a group stays if fewer than `keep` groups come before it (a larger score, or the same at a lower index)
-        for (int g = 0; g < n_groups; ++g) {
+        for (int g = lane; g < n_groups; g += 32) {
             int before = 0;
             for (int o = 0; o < n_groups; ++o) before += (g_s[o] > g_s[g] || (g_s[o] == g_s[g] && o < g)) ? 1 : 0;
             if (before >= keep)
                 for (int e = g * per; e < (g + 1) * per; ++e) c_s[e] = -INFINITY;
         }
+        __syncwarp();
     }
     for (int k = 0; k < top; ++k) {
-        int best = -1;
         float bv = -INFINITY;
-        for (int e = 0; e < n_experts; ++e) {
+        int best = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
             const float v = c_s[e];
-            if (v > bv) { best = e; bv = v; }          // false for minus infinity and for a taken expert's NaN
+            if (v > bv) { bv = v; best = e; }             // false for minus infinity and for a taken expert's NaN; rising e: the lower index stays
         }
-        if (best < 0) {                                   // fewer live experts than `top`: the lowest not yet taken, weight 0
-            for (int e = 0; e < n_experts && best < 0; ++e) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best, o);
+            if (ov > bv || (ov == bv && oe < best)) { bv = ov; best = oe; }
+        }
+        if (best == 0x7fffffff) {                         // fewer live experts than `top`: the lowest not yet taken, weight 0
+            best = 0;
+            for (int e = 0; e < n_experts; ++e) {
                 bool taken = false;
                 for (int j = 0; j < k; ++j) taken = taken || expert_of[(size_t)t * top + j] == e;
-                if (!taken) best = e;
+                if (!taken) { best = e; break; }
             }
-            expert_of[(size_t)t * top + k] = best < 0 ? 0 : best;
-            pair_weight[(size_t)t * top + k] = 0.f;
-            continue;
+            bv = -INFINITY;
         }
-        expert_of[(size_t)t * top + k] = best;
-        pair_weight[(size_t)t * top + k] = s_s[best] * scale;
-        c_s[best] = __int_as_float(0x7fc00000);           // taken: a NaN fails every comparison above
+        if (lane == 0) {
+            expert_of[(size_t)t * top + k] = best;
+            pair_weight[(size_t)t * top + k] = bv == -INFINITY ? 0.f : s_s[best] * scale;
+            c_s[best] = __int_as_float(0x7fc00000);       // taken
+        }
+        __syncwarp();
     }
 }
 
-SSB_API int ssb_route_sigmoid_groups(const void* x, int ldx, int dtype, const float* w, const float* correction,
-                                     const float* extra_w, int n_tokens, int width, int n_experts, int n_groups, int keep,
-                                     int top, float scale, int* expert_of, float* pair_weight, float* extra_out, int pdl,
-                                     cudaStream_t stream) {
+SSB_API int ssb_route_sigmoid_groups(const float* z, int ld, const float* correction, int n_tokens, int n_experts,
+                                     int n_groups, int keep, int top, float scale, int extra_col, int* expert_of,
+                                     float* pair_weight, float* extra_out, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (width <= 0 || n_experts <= 0 || n_groups <= 0 || n_experts % n_groups || keep < 1 || keep > n_groups || top < 1 ||
-        top > n_experts || n_experts > 4096 || (extra_w != nullptr && extra_out == nullptr))
+    if (n_experts <= 0 || n_groups <= 0 || n_experts % n_groups || keep < 1 || keep > n_groups || top < 1 ||
+        top > n_experts || n_experts > 2048 || ld < n_experts || extra_col >= ld || (extra_col >= 0 && extra_out == nullptr))
         return SSB_ERR_BAD_SIZE;
-    const size_t smem = (size_t)(2 * n_experts + n_groups) * sizeof(float);
-    int rc;
-    if (dtype == SSB_F32)
-        rc = ssb_launch(route_sigmoid_groups_kernel<float>, dim3(n_tokens), dim3(RG_THREADS), smem, stream, pdl != 0,
-                        (const float*)x, ldx, w, correction, extra_w, width, n_experts, n_groups, keep, top, scale, expert_of,
-                        pair_weight, extra_out);
-    else if (dtype == SSB_BF16)
-        rc = ssb_launch(route_sigmoid_groups_kernel<bf16>, dim3(n_tokens), dim3(RG_THREADS), smem, stream, pdl != 0,
-                        (const bf16*)x, ldx, w, correction, extra_w, width, n_experts, n_groups, keep, top, scale, expert_of,
-                        pair_weight, extra_out);
-    else
-        return SSB_ERR_BAD_DTYPE;
+    const size_t smem = (size_t)(RG_THREADS / 32) * (2 * n_experts + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(route_sigmoid_groups_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int rc = ssb_launch(route_sigmoid_groups_kernel, dim3((n_tokens + RG_THREADS / 32 - 1) / (RG_THREADS / 32)),
+                              dim3(RG_THREADS), smem, stream, pdl != 0, z, ld, correction, n_tokens, n_experts, n_groups, keep,
+                              top, scale, extra_col, expert_of, pair_weight, extra_out);
     return rc ? rc : ssb_launch_status();
 }
 

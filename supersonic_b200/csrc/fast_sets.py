@@ -188,22 +188,27 @@ class FastKernels(PlainKernels):
 
     def gate_up_swiglu(self, x, w_gate_up, layout, out, act=None, row_scale=None):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
-        if act is not None or row_scale is not None:
-            super().gate_up_swiglu(x, w_gate_up, layout, out, act, row_scale)
-            return
+        plain_gate = act is None and row_scale is None
         if layout == "interleaved":
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
+                # the unit's inner step (whichever it is) on the product's float32 sums, one rounding
                 if rows <= STREAM_ROWS and not self.deterministic:
-                    ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
+                    if plain_gate:
+                        ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
+                    else:
+                        ops.gemv_tc_gate(xt, w_gate_up, out, act, row_scale, pdl=self.pdl)
                 else:
                     n2 = w_gate_up.shape[0]
-                    ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU,
-                                tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n2) else self._tile_n(rows, n2))
+                    tile_n = ops.TC_TILE_PAIR if self._pair_tiles(rows, n2) else self._tile_n(rows, n2)
+                    if plain_gate:
+                        ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU, tile_n=tile_n)
+                    else:
+                        ops.gemm_tc_gate(xt, w_gate_up, out, act, row_scale, tile_n=tile_n)
                 return
-        if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
+        if plain_gate and layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
             return
-        super().gate_up_swiglu(x, w_gate_up, layout, out)
+        super().gate_up_swiglu(x, w_gate_up, layout, out, act, row_scale)
 
     # ---- attention -------------------------------------------------------------------
     def _buffer(self, name: str, n: int, dtype, device, zero=False) -> torch.Tensor:
@@ -456,14 +461,12 @@ class FastKernels(PlainKernels):
             super().grouped_linear(a, gather, top, w, out, scatter, groups)
 
     def expert_gate_up(self, x, top, w_gate_up, out, groups, act=None):
-        if act is not None:
-            super().expert_gate_up(x, top, w_gate_up, out, groups, act)
-        elif ops.grouped_gemm_mma_ok(x, w_gate_up, out, ops.GG_SWIGLU):
+        if ops.grouped_gemm_mma_ok(x, w_gate_up, out, ops.GG_SWIGLU):
             ops.grouped_gemm_mma(x, groups["order"], top, w_gate_up, out, None, groups["offsets"],
                                  groups["tile_expert"], groups["tile_row0"], groups["meta"], groups["max_tiles"],
-                                 ops.GG_SWIGLU, pdl=self.pdl)
+                                 ops.GG_SWIGLU, pdl=self.pdl, act=act)
         else:
-            super().expert_gate_up(x, top, w_gate_up, out, groups)
+            super().expert_gate_up(x, top, w_gate_up, out, groups, act)
 
     def expert_combine(self, residual, y, pair_weight, top):
         ops.expert_combine(residual, y, pair_weight, top, pdl=self.pdl)

@@ -43,6 +43,9 @@ struct TcRope {
     const float* sin_t;
     int max_pages, n_q, n_kv, head_dim, page_shift;
     float act_scale;           // modes TC_ACT + k: what the activation's result is multiplied by
+    int gate_kind;             // mode TC_SWIGLU: the gated unit's inner step (ssb_gate_fast) ...
+    float gate_limit;          // ... its clamp ...
+    const float* row_scale;    // ... and one factor per row of the result, or none
 };
 
 __device__ __forceinline__ void tc_store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
@@ -119,6 +122,7 @@ hi[4 * i4 + e] = a_ * sv + b_ * cv;                                             
             if (row >= M || n >= N) continue;
             if (mode == TC_SWIGLU) {
                 bf16* dst = (bf16*)C + (size_t)row * ldc + n / 2;
+                const float rs = rope.row_scale ? rope.row_scale[row] : 1.0f;
                 uint32_t packed[8];
     #pragma unroll
                 for (int g = 0; g < 2; ++g)
@@ -126,8 +130,8 @@ hi[4 * i4 + e] = a_ * sv + b_ * cv;                                             
                     for (int j = 0; j < 8; j += 2) {
                         const float g0 = __uint_as_float(r[g * 16 + j]), u0 = __uint_as_float(r[g * 16 + 8 + j]);
                         const float g1 = __uint_as_float(r[g * 16 + j + 1]), u1 = __uint_as_float(r[g * 16 + 9 + j]);
-                        __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
-                                                                  g1 / (1.0f + __expf(-g1)) * u1);
+                        __nv_bfloat162 v = __floats2bfloat162_rn(ssb_gate_fast(g0, u0, rope.gate_kind, rope.gate_limit) * rs,
+                                                                  ssb_gate_fast(g1, u1, rope.gate_kind, rope.gate_limit) * rs);
                         packed[g * 4 + j / 2] = *reinterpret_cast<uint32_t*>(&v);
                     }
                 if (n + 32 <= N) {
@@ -606,6 +610,17 @@ SSB_API int ssb_gemm_tc_act(const void* A, int lda, const void* W, int ldw, void
     TcRope extra{};
     extra.act_scale = scale;
     return gemm_tc_any(A, lda, W, ldw, C, ldc, SSB_BF16, M, N, K, TC_ACT + act, tile_n, 1, error_word, extra, stream);
+}
+
+// C (bfloat16, [M, N/2]) = gate_fn(A gate^T, A up^T) * row_scale with W's rows as [8 gate | 8 up] per 16: mode 2 with
+// another inner step of the gated unit (a kind of ssb_gate) and one float32 factor per row (or none).
+SSB_API int ssb_gemm_tc_gate(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                             int gate_kind, float gate_limit, const float* row_scale, int tile_n, int* error_word,
+                             cudaStream_t stream) {
+    if (gate_kind < 0 || gate_kind > SSB_GATE_CLAMPED_SWISH) return SSB_ERR_BAD_SIZE;
+    TcRope extra{};
+    extra.gate_kind = gate_kind; extra.gate_limit = gate_limit; extra.row_scale = row_scale;
+    return gemm_tc_any(A, lda, W, ldw, C, ldc, SSB_BF16, M, N, K, TC_SWIGLU, tile_n, 1, error_word, extra, stream);
 }
 
 SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,

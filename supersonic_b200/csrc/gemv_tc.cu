@@ -34,7 +34,7 @@ template <int BNB>                        // batch rows per tile: 16, 32, 64 or 
 __global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode, int splits,
-               float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
+               float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word, int gate_kind, float gate_limit, const float* __restrict__ row_scale) {
     constexpr int GV_STAGES = gv_stages(BNB);
     constexpr uint32_t W_BYTES = GV_BM * TC_BK * 2, X_BYTES = BNB * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = BNB < 32 ? 32 : BNB;
@@ -218,7 +218,10 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) up[j] = __shfl_down_sync(0xffffffffu, v[j0 + j], 8);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) act[j] = __fdividef(v[j0 + j], 1.0f + __expf(-v[j0 + j])) * up[j];
+                        for (int j = 0; j < 16; ++j) {
+                            act[j] = ssb_gate_fast(v[j0 + j], up[j], gate_kind, gate_limit);
+                            if (row_scale != nullptr && c0 + j0 + j < n_rows) act[j] *= row_scale[c0 + j0 + j];
+                        }
                         if (is_gate && n + 8 < N) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
@@ -251,7 +254,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <int BNB>
 static int launch_gv(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int out_is_f32, int n_rows,
                      int N, int K, int mode, int splits, float* partials, int* counters, int* error_word, bool pdl,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, int gate_kind = 0, float gate_limit = 0.f, const float* row_scale = nullptr) {
     constexpr int GV_STAGES = gv_stages(BNB);
     constexpr size_t smem = GV_STAGES * (GV_BM + BNB) * TC_BK * 2 + (2 * GV_STAGES + 1) * 8 + 32 + 1024;
     auto kern = gemv_tc_kernel<BNB>;
@@ -262,7 +265,8 @@ static int launch_gv(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
         configured = true;
     }
     const int rc = ssb_launch(kern, dim3((N + GV_BM - 1) / GV_BM, splits), dim3(GV_THREADS), smem, stream, pdl, mw, mx,
-                              out, ldo, out_is_f32, n_rows, N, K, mode, splits, partials, counters, error_word);
+                              out, ldo, out_is_f32, n_rows, N, K, mode, splits, partials, counters, error_word, gate_kind, gate_limit,
+                              row_scale);
     return rc ? rc : ssb_launch_status();
 }
 
@@ -278,9 +282,10 @@ SSB_API int ssb_gemv_tc_counters(int N) { return (N + GV_BM - 1) / GV_BM; }
 
 // x: bfloat16 [n_rows <= 128, K]; W: bfloat16 [N, K]; modes as ssb_gemm_tc.  splits: blocks that
 // share the K range of a row tile (1 = none).
-SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int out_dtype,
-                        int n_rows, int N, int K, int mode, int splits, float* partials, int* counters,
-                        int* error_word, int pdl, cudaStream_t stream) {
+static int gemv_tc_any(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int out_dtype,
+                       int n_rows, int N, int K, int mode, int splits, float* partials, int* counters,
+                       int* error_word, int pdl, cudaStream_t stream, int gate_kind, float gate_limit,
+                       const float* row_scale) {
     if (n_rows <= 0 || N <= 0) return 0;
     if (n_rows > GV_MAX_ROWS || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !error_word || splits < 1) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)partials) & 15) return SSB_ERR_BAD_SIZE;
@@ -295,8 +300,24 @@ SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* ou
     rc = make_map(&mx, x, n_rows, K, ldx, bnb);
     if (rc) return rc;
     const int f32o = out_dtype == SSB_F32;
-    if (bnb == 16) return launch_gv<16>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
-    if (bnb == 32) return launch_gv<32>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
-    if (bnb == 64) return launch_gv<64>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
-    return launch_gv<128>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
+    if (bnb == 16) return launch_gv<16>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream, gate_kind, gate_limit, row_scale);
+    if (bnb == 32) return launch_gv<32>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream, gate_kind, gate_limit, row_scale);
+    if (bnb == 64) return launch_gv<64>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream, gate_kind, gate_limit, row_scale);
+    return launch_gv<128>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream, gate_kind, gate_limit, row_scale);
+}
+
+SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int out_dtype,
+                        int n_rows, int N, int K, int mode, int splits, float* partials, int* counters,
+                        int* error_word, int pdl, cudaStream_t stream) {
+    return gemv_tc_any(x, ldx, W, ldw, out, ldo, out_dtype, n_rows, N, K, mode, splits, partials, counters, error_word, pdl,
+                       stream, SSB_GATE_SILU, 0.f, nullptr);
+}
+
+// mode 2 with another inner step of the gated unit (a kind of ssb_gate) and one float32 factor per row of x (or none)
+SSB_API int ssb_gemv_tc_gate(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int n_rows, int N, int K,
+                             int gate_kind, float gate_limit, const float* row_scale, int* error_word, int pdl,
+                             cudaStream_t stream) {
+    if (gate_kind < 0 || gate_kind > SSB_GATE_CLAMPED_SWISH) return SSB_ERR_BAD_SIZE;
+    return gemv_tc_any(x, ldx, W, ldw, out, ldo, SSB_BF16, n_rows, N, K, TC_SWIGLU, 1, nullptr, nullptr, error_word, pdl,
+                       stream, gate_kind, gate_limit, row_scale);
 }

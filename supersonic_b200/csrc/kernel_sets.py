@@ -307,10 +307,10 @@ class PlainKernels:
     def route_table(self, token_ids, table, n_experts, expert_of, pair_weight):
         ops.route_table(token_ids, table, n_experts, expert_of, pair_weight)
 
-    def route_sigmoid_groups(self, x, weight, correction, extra_weight, n_groups, keep, scale, expert_of, pair_weight,
-                             extra_out=None):
-        ops.route_sigmoid_groups(x, weight, correction, extra_weight, n_groups, keep, scale, expert_of, pair_weight,
-                                 extra_out, pdl=self._chain(x.shape[0]))
+    def route_sigmoid_groups(self, logits, n_experts, correction, n_groups, keep, scale, expert_of, pair_weight,
+                             extra_col=None, extra_out=None):
+        ops.route_sigmoid_groups(logits, n_experts, correction, n_groups, keep, scale, expert_of, pair_weight, extra_col,
+                                 extra_out, pdl=self._chain(logits.shape[0]))
 
     def group_by_expert(self, expert_of, n_experts, groups):
         """``groups``: the dict of int32 tensors a grouped product reads (offsets, order, tile_expert,

@@ -436,9 +436,13 @@ def grouped_gemm_mma_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mod
 def grouped_gemm_mma(a: torch.Tensor, a_index: Optional[torch.Tensor], a_div: int, w: torch.Tensor,
                      out: torch.Tensor, c_index: Optional[torch.Tensor], offsets: torch.Tensor,
                      tile_expert: torch.Tensor, tile_row0: torch.Tensor, meta: torch.Tensor, max_tiles: int,
-                     mode: int = GG_STORE, pdl: bool = False) -> None:
+                     mode: int = GG_STORE, pdl: bool = False, act=None) -> None:
     """``grouped_gemm_plain`` on mma.sync (tiles of 64 rows).  mode GG_SWIGLU: ``w`` [E, 2N, K] holds gate rows then
-    up rows and ``out`` [rows, N] gets silu(a gate^T) * (a up^T)."""
+    up rows and ``out`` [rows, N] gets silu(a gate^T) * (a up^T), or with ``act`` = (kind, limit) that inner step of
+    the gated unit (``gated_activation``)."""
+    kind, limit = act if act else ("silu", 0.0)
+    if kind not in GATE_KINDS_FF:
+        raise KernelError(f"grouped_gemm_mma: gate {kind!r} is not known (known: {sorted(GATE_KINDS_FF)})")
     E, n_w, K = w.shape
     N = n_w // 2 if mode == GG_SWIGLU else n_w
     if not grouped_gemm_mma_ok(a, w, out, mode) or a.shape[1] != K or out.shape[1] != N:
@@ -447,7 +451,7 @@ def grouped_gemm_mma(a: torch.Tensor, a_index: Optional[torch.Tensor], a_div: in
         _ptr(a), c_int(a.stride(0)), _ptr(a_index), c_int(a_div), _ptr(w), c_int(K), c_longlong(n_w * K), _ptr(out),
         c_int(out.stride(0)), _ptr(c_index), c_int(dtype_code(out.dtype)), _ptr(offsets), _ptr(tile_expert),
         _ptr(tile_row0), _ptr(meta), c_int(max_tiles), c_int(order_rows(a, a_index, out, c_index)), c_int(N), c_int(K),
-        c_int(mode), c_int(1 if pdl else 0), _stream()), "grouped_gemm_mma")
+        c_int(mode), c_int(GATE_KINDS_FF[kind]), c_float(limit), c_int(1 if pdl else 0), _stream()), "grouped_gemm_mma")
 
 
 # ---- linear recurrences ----------------------------------------------------------------
@@ -1234,33 +1238,31 @@ def route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int, ex
         _ptr(pair_weight), c_int(T), c_int(1 if pdl else 0), _stream()), "route_table")
 
 
-def route_sigmoid_groups(x: torch.Tensor, weight: torch.Tensor, correction: Optional[torch.Tensor],
-                         extra_weight: Optional[torch.Tensor], n_groups: int, keep: int, scale: float,
-                         expert_of: torch.Tensor, pair_weight: torch.Tensor, extra_out: Optional[torch.Tensor] = None,
-                         pdl: bool = False) -> None:
-    """Per token: s = sigmoid(weight @ x) in float32; the ``top`` experts with the largest s + correction among the
-    experts of the ``keep`` best of ``n_groups`` equal groups of neighbours (a group's score: the sum of its two
-    largest s + correction); pair_weight = s * scale of the chosen.  ``extra_weight`` [1, width]: its sigmoid per
-    token into ``extra_out``."""
-    _need(x, "x", None, 2); _need(weight, "weight", torch.float32, 2)
+def route_sigmoid_groups(logits: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor], n_groups: int, keep: int,
+                         scale: float, expert_of: torch.Tensor, pair_weight: torch.Tensor, extra_col: Optional[int] = None,
+                         extra_out: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """Per token, from float32 router logits [tokens, >= n_experts]: s = sigmoid(z); the ``top`` experts with the
+    largest s + correction among the experts of the ``keep`` best of ``n_groups`` equal groups of neighbours (a
+    group's score: the sum of its two largest s + correction); pair_weight = s * scale of the chosen.  ``extra_col``:
+    a further column whose sigmoid per token goes to ``extra_out``."""
+    _need(logits, "logits", torch.float32, 2)
     _need(expert_of, "expert_of", torch.int32, 2); _need(pair_weight, "pair_weight", torch.float32, 2)
-    T, W = x.shape
-    E, top = weight.shape[0], expert_of.shape[1]
-    if weight.shape[1] != W or not weight.is_contiguous() or tuple(expert_of.shape) != (T, top) \
-            or tuple(pair_weight.shape) != (T, top) or not (expert_of.is_contiguous() and pair_weight.is_contiguous()):
-        raise KernelError("route_sigmoid_groups: weight [experts, width]; expert_of and pair_weight [tokens, top], contiguous")
+    T, top = logits.shape[0], expert_of.shape[1]
+    if logits.shape[1] < n_experts or tuple(expert_of.shape) != (T, top) or tuple(pair_weight.shape) != (T, top) \
+            or not (expert_of.is_contiguous() and pair_weight.is_contiguous()):
+        raise KernelError("route_sigmoid_groups: logits [tokens, >= experts]; expert_of and pair_weight [tokens, top], contiguous")
     if correction is not None:
         _need(correction, "correction", torch.float32, 1)
-        if correction.shape[0] != E:
+        if correction.shape[0] != n_experts:
             raise KernelError("route_sigmoid_groups: one correction per expert")
-    if extra_weight is not None:
-        _need(extra_weight, "extra_weight", torch.float32); _need(extra_out, "extra_out", torch.float32, 1)
-        if extra_weight.numel() != W or not extra_weight.is_contiguous() or extra_out.shape[0] != T:
-            raise KernelError("route_sigmoid_groups: the extra row has the input's width, its result one number per token")
+    if extra_col is not None:
+        _need(extra_out, "extra_out", torch.float32, 1)
+        if not 0 <= extra_col < logits.shape[1] or extra_out.shape[0] != T:
+            raise KernelError("route_sigmoid_groups: the extra column lies in the logits' rows, its result is one number per token")
     _check(_fn("expert_ops", "ssb_route_sigmoid_groups")(
-        _ptr(x), c_int(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(weight), _ptr(correction), _ptr(extra_weight), c_int(T),
-        c_int(W), c_int(E), c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _ptr(expert_of), _ptr(pair_weight),
-        _ptr(extra_out if extra_weight is not None else None), c_int(1 if pdl else 0), _stream()), "route_sigmoid_groups")
+        _ptr(logits), c_int(logits.stride(0)), _ptr(correction), c_int(T), c_int(n_experts), c_int(n_groups), c_int(keep),
+        c_int(top), c_float(scale), c_int(-1 if extra_col is None else extra_col), _ptr(expert_of), _ptr(pair_weight),
+        _ptr(extra_out if extra_col is not None else None), c_int(1 if pdl else 0), _stream()), "route_sigmoid_groups")
 
 
 def expert_tiles_bound(n_pairs: int, n_experts: int, tile_rows: int) -> int:
@@ -1701,6 +1703,37 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")
 
 
+def _gate_args(act, row_scale, rows: int, what: str):
+    kind, limit = act if act else ("silu", 0.0)
+    if kind not in GATE_KINDS_FF:
+        raise KernelError(f"{what}: gate {kind!r} is not known (known: {sorted(GATE_KINDS_FF)})")
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32, 1)
+        if row_scale.shape[0] != rows:
+            raise KernelError(f"{what}: one factor per row")
+    return GATE_KINDS_FF[kind], float(limit)
+
+
+def gemm_tc_gate(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act=None, row_scale: Optional[torch.Tensor] = None,
+                 tile_n: Optional[int] = None) -> None:
+    """out = f(a @ gate^T, a @ up^T) * row_scale on the tensor cores, the inner step on the float32 sums; ``w``'s rows
+    come as [8 gate | 8 up] per 16; ``act`` = (kind, limit) as in :func:`gated_activation`, None for silu(g) u."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N // 2):
+        raise KernelError(f"gemm_tc_gate: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    kind, limit = _gate_args(act, row_scale, M, "gemm_tc_gate")
+    if tile_n is None:
+        tile_n = 256 if N > 128 else 128
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemm_tc", "ssb_gemm_tc_gate")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N),
+        c_int(K), c_int(kind), c_float(limit), _ptr(row_scale), c_int(tile_n), _ptr(tc_error_word(a.device)), _stream()),
+        "gemm_tc_gate")
+
+
 def gemm_tc_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str, scale: float = 1.0,
                 tile_n: Optional[int] = None) -> None:
     """out (bfloat16) = act(a @ w^T) * scale on the tensor cores: the activation (a kind of ``ACTIVATIONS``) is taken
@@ -1877,6 +1910,23 @@ def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         c_int(dtype_code(out.dtype)), c_int(B), c_int(N), c_int(K), c_int(mode), c_int(splits),
         _ptr(partials), _ptr(counters), _ptr(tc_error_word(x.device)), c_int(1 if pdl else 0), _stream()),
         "gemv_tc")
+
+
+def gemv_tc_gate(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act=None, row_scale: Optional[torch.Tensor] = None,
+                 pdl: bool = False) -> None:
+    """:func:`gemm_tc_gate` for up to 128 rows, the weights on the M side of the MMA."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    B, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (B, N // 2) or B > GEMV_TC_MAX_ROWS:
+        raise KernelError(f"gemv_tc_gate: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    kind, limit = _gate_args(act, row_scale, B, "gemv_tc_gate")
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemv_tc", "ssb_gemv_tc_gate")(
+        _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(N),
+        c_int(K), c_int(kind), c_float(limit), _ptr(row_scale), _ptr(tc_error_word(x.device)), c_int(1 if pdl else 0),
+        _stream()), "gemv_tc_gate")
 
 
 # ---- vector element-wise kernels ------------------------------------------------------------------

@@ -63,9 +63,10 @@ class TableRouter:
 @register_router("sigmoid_groups")
 class SigmoidGroupRouter:
     """params: ``groups`` (1), ``keep`` (all groups), ``scale`` (1.0); weights: ``weight`` [experts, hidden],
-    ``correction`` [experts] (optional).  The logits are float32 sums over float32 copies of the stored weights.
-    ``extra`` (set by the part that owns the router): one more row whose sigmoid per token the router's kernel
-    writes along the way."""
+    ``correction`` [experts] (optional).  The logits are a product of their own with a float32 result (in the
+    bfloat16 path: bfloat16 operands, whose products are exact in float32, summed in float32).  ``add_row`` (called
+    by the part that owns the router) lets one more row ride along in that product; its sigmoid per token is
+    written by the router's kernel."""
 
     def __init__(self, params, weights, build: BuildContext, n_experts: int, top: int):
         self.n_experts, self.top = n_experts, top
@@ -77,19 +78,34 @@ class SigmoidGroupRouter:
         if top > self.keep * (n_experts // self.groups):
             raise ValueError(f"sigmoid_groups: {top} experts a token cannot come from {self.keep} groups of "
                              f"{n_experts // self.groups}")
-        self.weight = build.weights.stored(weights["weight"]).float().contiguous()
-        if self.weight.dim() != 2 or self.weight.shape[0] != n_experts:
-            raise ValueError(f"{weights['weight']} has shape {tuple(self.weight.shape)}, expected [{n_experts}, hidden]")
+        self.rows = [build.weights.as_dtype(weights["weight"], build.dtype)]
+        if self.rows[0].dim() != 2 or self.rows[0].shape[0] != n_experts:
+            raise ValueError(f"{weights['weight']} has shape {tuple(self.rows[0].shape)}, expected [{n_experts}, hidden]")
         self.correction = None
         if weights.get("correction"):
             self.correction = build.weights.stored(weights["correction"]).float().contiguous()
             if tuple(self.correction.shape) != (n_experts,):
                 raise ValueError(f"{weights['correction']} has shape {tuple(self.correction.shape)}, expected ({n_experts},)")
-        self.extra = None
+        self.extra_col = None
+        self._pack()
+
+    def _pack(self):
+        w = torch.cat(self.rows, dim=0)
+        pad = (-w.shape[0]) % 8                  # rows of the product's result stay a multiple of 8 wide
+        if pad:
+            w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
+        self.weight = w.contiguous()
+
+    def add_row(self, row: torch.Tensor) -> None:
+        self.rows.append(row.reshape(1, -1).to(self.rows[0].dtype))
+        self.extra_col = self.n_experts
+        self._pack()
 
     def route(self, ctx, x, expert_of, pair_weight, extra_out=None):
-        ctx.kernels.route_sigmoid_groups(x, self.weight, self.correction, self.extra if extra_out is not None else None,
-                                         self.groups, self.keep, self.scale, expert_of, pair_weight, extra_out)
+        logits = torch.empty((x.shape[0], self.weight.shape[0]), dtype=torch.float32, device=x.device)
+        ctx.kernels.linear(x, self.weight, logits)
+        ctx.kernels.route_sigmoid_groups(logits, self.n_experts, self.correction, self.groups, self.keep, self.scale,
+                                         expert_of, pair_weight, self.extra_col if extra_out is not None else None, extra_out)
 
 
 @register_feed_forward("experts")
@@ -122,20 +138,21 @@ class Experts:
         self.router = ROUTERS[router["kind"]](router, weights, build, self.E, self.top)
         from .feed_forward import SwiGLU, gated_activation_of
         self.act = gated_activation_of(params.get("activation"))
-        self.shared, self.shared_gate = None, None
+        self.shared, self.shared_gate = None, False
         if params.get("shared"):
             sh = params["shared"]
             self.shared = SwiGLU({"hidden_size": self.hidden, "intermediate_size": int(sh["intermediate_size"]),
                                   "activation": sh.get("activation")},
                                  {r: weights[f"shared.{r}"] for r in ("gate", "up", "down")}, build)
             if sh.get("gate"):
-                sg = w.stored(weights["shared.sg"]).float().reshape(-1).contiguous()
+                sg = w.stored(weights["shared.sg"]).reshape(-1)
                 if sg.numel() != self.hidden:
                     raise ValueError(f"{weights['shared.sg']} has {sg.numel()} values, expected {self.hidden}")
-                if not hasattr(self.router, "extra"):
+                if not hasattr(self.router, "add_row"):
                     raise ValueError(f"experts: the router {router['kind']!r} reads no activations, so it cannot take the "
                                      "shared expert's gate along")
-                self.shared_gate = self.router.extra = sg     # the router's kernel reads the token anyway: it takes this row too
+                self.router.add_row(sg)          # the router's product reads the token anyway: it takes this row too
+                self.shared_gate = True
         self.dtype = dt
 
     @staticmethod
@@ -152,7 +169,7 @@ class Experts:
         expert_of = torch.empty((T, top), dtype=torch.int32, device=dev)
         pair_weight = torch.empty((T, top), dtype=torch.float32, device=dev)
         shared_scale = None
-        if self.shared_gate is not None:
+        if self.shared_gate:
             shared_scale = torch.empty(T, dtype=torch.float32, device=dev)
             self.router.route(ctx, xt, expert_of, pair_weight, extra_out=shared_scale)
         else:
