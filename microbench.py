@@ -275,7 +275,8 @@ def sigmoid_attention(args):
     kc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
     vc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
     table = (torch.arange(B * pages, dtype=torch.int32, device=DEV) + 1).view(B, pages).contiguous()
-    q = (torch.randn(B * T, H * d, device=DEV) * 0.5).bfloat16()
+    q = (torch.randn(B * T, H * d + 8 * ((H + 7) // 8), device=DEV) * 0.5).bfloat16()
+    gate = q[:, H * d:] if args.gate else None
     start = ctx - T
     pos = (torch.arange(T, dtype=torch.int32, device=DEV) + start).repeat(B)
     slot = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(T)
@@ -299,13 +300,17 @@ def sigmoid_attention(args):
 def window_attention(args):
     """Softmax attention over a window of --window tokens with --keep kept first tokens or pooled runs of --pool
     tokens, scores capped at --cap, values turned (--turn): --seqs prompts of --tokens tokens (or, with --tokens 1,
-    decode steps at --context), --heads over --kv-heads heads of --head-dim."""
-    H, G, d, B, T, ps = args.heads, args.kv_heads, args.head_dim, args.seqs, args.tokens, 6
+    decode steps at --context), --heads over --kv-heads heads of --head-dim.  --maps 2: two score maps a head over
+    the same values of --vdim (twice the query and key heads, two key heads a value head); --gate: a sigmoid gate per
+    head and token.  --window 0: every earlier token."""
+    M = args.maps
+    H, G, d, B, T, ps = args.heads * M, args.kv_heads * M, args.head_dim, args.seqs, args.tokens, 6
+    dv = args.vdim or d
     W, P, F = args.window, args.pool, args.keep
     ctx = args.context if T == 1 else T
     pages = -(-ctx // 64)
     kc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
-    vc = (torch.randn(B * pages + 1, G, 64, d, device=DEV) * 0.5).bfloat16()
+    vc = (torch.randn(B * pages + 1, G // M, 64, dv, device=DEV) * 0.5).bfloat16()
     table = (torch.arange(B * pages, dtype=torch.int32, device=DEV) + 1).view(B, pages).contiguous()
     pooled = None
     if P:
@@ -313,7 +318,8 @@ def window_attention(args):
         pooled = ((torch.randn(B * pp + 1, G, 64, d, device=DEV) * 0.5).bfloat16(),
                   (torch.randn(B * pp + 1, G, 64, d, device=DEV) * 0.5).bfloat16(),
                   (torch.arange(B * pp, dtype=torch.int32, device=DEV) + 1).view(B, pp).contiguous())
-    q = (torch.randn(B * T, H * d, device=DEV) * 0.5).bfloat16()
+    q = (torch.randn(B * T, H * d + 8 * ((H + 7) // 8), device=DEV) * 0.5).bfloat16()
+    gate = q[:, H * d:] if args.gate else None
     start = ctx - T
     pos = (torch.arange(T, dtype=torch.int32, device=DEV) + start).repeat(B)
     slot = torch.arange(B, dtype=torch.int32, device=DEV).repeat_interleave(T)
@@ -324,20 +330,35 @@ def window_attention(args):
     if args.turn:
         angle = torch.arange(ctx, device=DEV).float()[:, None] * (10000.0 ** (-torch.arange(d // 2, device=DEV).float() * 2 / d))
         vcos, vsin = angle.cos().contiguous(), angle.sin().contiguous()
-    out = torch.empty(B * T, H * d, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(B * T, H * dv, device=DEV, dtype=torch.bfloat16)
     cap, sink = (args.cap or None), (True if F else None)
     if args.kernel == "plain":
-        fn = lambda i: ops.window_attention_plain(q, kc, vc, table, pooled, pos, slot, out, H, G, d, d, ps, W, F, P, d ** -0.5,
-                                                  cap, sink, vcos, vsin, False)
+        fn = lambda i: ops.window_attention_plain(q, kc, vc, table, pooled, pos, slot, out, H, G, d, dv, ps, W, F, P, d ** -0.5,
+                                                  cap, sink, vcos, vsin, False, v_share=M, gate=gate)
     else:
-        fn = lambda i: ops.window_attention_mma(q, kc, vc, table, pooled, cu, seq_start, seq_slot, out, T, H, G, d, d, ps, W, F,
-                                                P, d ** -0.5, cap, sink, vcos, vsin, False)
+        fn = lambda i: ops.window_attention_mma(q, kc, vc, table, pooled, cu, seq_start, seq_slot, out, T, H, G, d, dv, ps, W, F,
+                                                P, d ** -0.5, cap, sink, vcos, vsin, False, v_share=M, gate=gate)
     us = _time(fn, args.iters)
-    lo = lambda p: max(0, p - W + 1)
+    lo = lambda p: max(0, p - W + 1) if W else 0
     pairs = sum(p - lo(p) + 1 + (lo(p) // P if P else min(F, lo(p))) for p in range(start, ctx)) * B
     return {"kernel": "window_attention_" + ("plain" if args.kernel == "plain" else "mma"), "seqs": B, "tokens": T,
-            "context": ctx, "window": W, "pool": P, "keep": F, "us": round(us, 2),
-            "TFLOP/s": round(4.0 * pairs * H * d / us / 1e6, 2)}
+            "context": ctx, "window": W, "pool": P, "keep": F, "maps": M, "us": round(us, 2),
+            "TFLOP/s": round(2.0 * pairs * H * (d + dv) / us / 1e6, 2)}
+
+
+def norm_add(args):
+    """A sublayer's float32 result normed, added to the stream and zeroed behind the read, with (--kernel next) or
+    without the next sublayer's normed rows written in the same pass: --rows tokens of width --n."""
+    T, Wd = args.rows, args.n
+    res = [torch.randn(T, Wd, device=DEV) for _ in range(4)]          # four sets in turn: larger than L2 at real sizes
+    br = [torch.randn(T, Wd, device=DEV) for _ in range(4)]
+    w1, w2 = torch.randn(Wd, device=DEV), torch.randn(Wd, device=DEV)
+    nxt = torch.empty(T, Wd, device=DEV, dtype=torch.bfloat16) if args.kernel == "next" else None
+    us = _time(lambda i: ops.rms_add(res[i % 4], br[i % 4], w1, 1e-6, clear=True, next_weight=w2 if nxt is not None else None,
+                                     next_eps=1e-6, next_out=nxt), args.iters)
+    nbytes = T * Wd * (16 + (2 if nxt is not None else 0))
+    return {"kernel": "rms_add" + ("_next" if nxt is not None else ""), "rows": T, "width": Wd, "us": round(us, 2),
+            "GB/s": round(nbytes / us / 1e3, 1)}
 
 
 def mingru_scan(args):
@@ -379,7 +400,7 @@ def main(argv=None):
     sub = ap.add_subparsers(dest="what", required=True)
     for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling", "latent_attention", "grouped_gemm",
                  "gated_linear_scan", "matrix_state_scan", "gated_unit_scan", "sigmoid_attention", "window_attention",
-                 "mingru_scan"):
+                 "mingru_scan", "norm_add"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--heads", type=int, default=32)
@@ -417,6 +438,9 @@ def main(argv=None):
         p.add_argument("--keep", type=int, default=0, help="window_attention: kept first tokens (with a sink)")
         p.add_argument("--cap", type=float, default=0.0, help="window_attention: score cap (0: none)")
         p.add_argument("--turn", action="store_true", help="window_attention: values stored turned by their position")
+        p.add_argument("--maps", type=int, default=1, help="window_attention: score maps a head (2: over the same values)")
+        p.add_argument("--vdim", type=int, default=0, help="window_attention: width of a value row (0: the head size)")
+        p.add_argument("--gate", action="store_true", help="window_attention: a sigmoid gate per head and token")
     args = ap.parse_args(argv)
     print(json.dumps(globals()[args.what](args)))
 

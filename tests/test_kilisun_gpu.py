@@ -54,17 +54,11 @@ def close(got, ref, dtype, what=""):
 
 
 def build_for(name, dtype):
-    """The configuration's weights; for bfloat16 with the routers' corrections spread eight times as wide.  Random
-    routers leave several tokens in a hundred with two experts (or two groups) within a hundredth of each other;
-    bfloat16 then picks the other one for some of them, the plain statement's logits there are no longer the
-    answer, and through the keys such a token leaves neither are those behind it.  Wider corrections keep the
-    choice a function of the token (the scores still order the experts within their reach) and leave the margins
-    that rounding cannot cross.  float32 runs keep the routers as drawn."""
+    """The configuration's weights; for bfloat16 with decisive routers (``tiny_kilisun.decisive``), so that a token's
+    experts do not hang on the rounding of a score.  float32 runs keep the routers as drawn."""
     cfg, store, plain = tk.build(name)
-    if dtype == torch.float32:
-        return cfg, store, plain
-    wide = {n.replace(".", "__"): t.float() * 8.0 for n, t in plain.items() if n.endswith(".correction")}
-    store, plain = tk.changed(plain, **wide)
+    if dtype != torch.float32:
+        store, plain = tk.decisive(plain)
     return cfg, store, plain
 
 

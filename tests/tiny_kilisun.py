@@ -109,3 +109,13 @@ def changed(plain, **changes):
         name = k.replace("__", ".")
         t[name] = v.to(t[name].dtype)
     return WeightStore.from_tensors(t), t
+
+
+def decisive(plain, factor=8.0):
+    """(weight store, weights by name) with the routers' corrections spread ``factor`` times as wide.  Random routers
+    leave several tokens in a hundred with two experts (or two groups) within a hundredth of each other; bfloat16
+    then picks the other one for some of them, the plain statement's logits there are no longer the answer, and
+    through the keys such a token leaves neither are those behind it.  Wider corrections keep the choice a function
+    of the token (the scores still order the experts within their reach) and leave margins that rounding cannot
+    cross."""
+    return changed(plain, **{n.replace(".", "__"): t.float() * factor for n, t in plain.items() if n.endswith(".correction")})
