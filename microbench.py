@@ -348,18 +348,16 @@ def window_attention(args):
 
 def norm_add(args):
     """A sublayer's float32 result normed, added to the stream and zeroed behind the read, with (--kernel next) or
-    without the next sublayer's normed rows written in the same pass: --rows tokens of width --n.  --splits 1: the
-    weights four bytes off a 16-byte boundary, which makes the kernel take one column a thread and access."""
+    without the next sublayer's normed rows written in the same pass: --rows tokens of width --n."""
     T, Wd = args.rows, args.n
     res = [torch.randn(T, Wd, device=DEV) for _ in range(4)]          # four sets in turn: larger than L2 at real sizes
     br = [torch.randn(T, Wd, device=DEV) for _ in range(4)]
-    off = 1 if args.splits == 1 else 0
-    w1, w2 = torch.randn(Wd + 4, device=DEV)[off:off + Wd], torch.randn(Wd + 4, device=DEV)[off:off + Wd]
+    w1, w2 = torch.randn(Wd, device=DEV), torch.randn(Wd, device=DEV)
     nxt = torch.empty(T, Wd, device=DEV, dtype=torch.bfloat16) if args.kernel == "next" else None
     us = _time(lambda i: ops.rms_add(res[i % 4], br[i % 4], w1, 1e-6, clear=True, next_weight=w2 if nxt is not None else None,
                                      next_eps=1e-6, next_out=nxt), args.iters)
     nbytes = T * Wd * (16 + (2 if nxt is not None else 0))
-    return {"kernel": "rms_add" + ("_next" if nxt is not None else "") + ("_scalar" if off else ""), "rows": T, "width": Wd, "us": round(us, 2),
+    return {"kernel": "rms_add" + ("_next" if nxt is not None else ""), "rows": T, "width": Wd, "us": round(us, 2),
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
