@@ -532,7 +532,7 @@ template <typename T>
 __global__ void __launch_bounds__(RA_THREADS)
 rms_add_kernel(float* __restrict__ residual, float* __restrict__ branch, const float* __restrict__ w, float eps, int width,
                int clear, const float* __restrict__ next_w, float next_eps, T* __restrict__ next_out) {
-    extern __shared__ float ra_row[];                     // the branch's row, then the stream's
+    extern __shared__ float ra_row[];
     __shared__ float red[RA_THREADS / 32];
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();
@@ -540,13 +540,11 @@ rms_add_kernel(float* __restrict__ residual, float* __restrict__ branch, const f
     const int tid = threadIdx.x;
     float* br = branch + t * width;
     float* rr = residual + t * width;
-    float* ra_res = ra_row + width;
-    // both rows are asked for before anything waits: the stream's row is under way while the branch's sum is taken
-    // (four-byte accesses a thread: with sixteen the same kernel took 87 us instead of 33 for 2,048 rows of 2,048)
+    // four-byte accesses a thread, the stream's row read behind the branch's sum: 33 us for 2,048 rows of 2,048; with
+    // sixteen-byte accesses the same kernel took 87 us, with both rows staged in shared memory up front 49
     float sq = 0.f;
     for (int c = tid; c < width; c += RA_THREADS) {
         const float v = br[c];
-        ra_res[c] = rr[c];
         ra_row[c] = v;
         sq = fmaf(v, v, sq);
         if (clear) br[c] = 0.f;
@@ -554,23 +552,23 @@ rms_add_kernel(float* __restrict__ residual, float* __restrict__ branch, const f
     const float inv = 1.0f / sqrtf(ra_block_sum(sq, red) / (float)width + eps);
     float sq2 = 0.f;
     for (int c = tid; c < width; c += RA_THREADS) {
-        const float v = ra_res[c] + ra_row[c] * inv * w[c];
+        const float v = rr[c] + ra_row[c] * inv * w[c];
         rr[c] = v;
-        ra_res[c] = v;
+        ra_row[c] = v;
         sq2 = fmaf(v, v, sq2);
     }
     if (next_out == nullptr) return;
     const float inv2 = 1.0f / sqrtf(ra_block_sum(sq2, red) / (float)width + next_eps);
     for (int c = tid; c < width; c += RA_THREADS)
-        next_out[t * width + c] = ssb_from_float<T>(ra_res[c] * inv2 * next_w[c]);
+        next_out[t * width + c] = ssb_from_float<T>(ra_row[c] * inv2 * next_w[c]);
 }
 
 SSB_API int ssb_rms_add(float* residual, float* branch, const float* w, float eps, int n_tokens, int width, int clear,
                         const float* next_w, float next_eps, void* next_out, int next_dtype, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (width <= 0 || (size_t)width * 2 * sizeof(float) > 200 * 1024 || (next_out != nullptr && next_w == nullptr))
+    if (width <= 0 || (size_t)width * sizeof(float) > 200 * 1024 || (next_out != nullptr && next_w == nullptr))
         return SSB_ERR_BAD_SIZE;
-    const size_t smem = (size_t)width * 2 * sizeof(float);
+    const size_t smem = (size_t)width * sizeof(float);
     int rc;
 #define SSB_RA(TYPE)                                                                                                 \
     {                                                                                                                \
