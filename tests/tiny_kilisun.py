@@ -66,7 +66,7 @@ _a = [moe(diff(6, 3, 10, 14, 9, 6, 300.0, 0.3, softcap=7.0, scale=0.4), 12, 3, 4
 A = model(97, 44, 1e-5, _a + [moe(reader(_a, 0, size=30), 6, 1, 1, 1, 12, 0.8, 0.7), dense(conv(5, 5, 8, 2, 0.2, 1), 26, 1.1)])
 
 # round sizes, which every fast kernel takes; a reader with a shorter window and other query heads than its writer
-_b = [dense(conv(4, 2, 64, 3, 0.25, 32), 128, 1.5),
+_b = [dense(conv(8, 2, 64, 5, 0.25, 32), 128, 1.75),
       moe(diff(4, 2, 64, 128, 100, 32, 10000.0, 0.5, softcap=30.0), 8, 2, 4, 2, 64, 1.25, 1.75, shared=(64, 1.5)),
       moe(diff(2, 1, 128, 64, 70, 128, 5000.0, 0.2), 16, 4, 4, 3, 64, 2.5, 1.0)]
 B = model(256, 128, 1e-6, _b + [dense(reader(_b, 1, size=40, heads=8), 256, 3.0), dense(conv(8, 1, 128, 2, 0.5, 7), None, 1.0),
